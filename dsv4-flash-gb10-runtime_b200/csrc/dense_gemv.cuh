@@ -1,0 +1,216 @@
+// Dense M=1 GEMV over a quantized weight matrix, shared by the MXFP4 and FP8-E4M3 libraries.
+//   y[n] = bf16( sum_k W[n,k] * x[k] ),  FP32 accumulation across blocks.
+// A CTA owns a contiguous range of output rows; a warp owns one 32-block slice of the reduction axis
+// (1024 MXFP4 elements / 512 FP8 elements) and walks down the CTA's rows with 8 row loads in flight
+// per lane and the next 8 already requested.  Per-slice partial sums meet in shared memory.
+#pragma once
+
+#include "gemv_engine.cuh"
+
+#include <cstdio>
+#include <cstdlib>
+#include <utility>
+
+namespace dsv4 {
+
+constexpr int kDenseThreads = 256;
+constexpr int kDenseRows = 8;          // rows per warp batch
+constexpr int kDenseCap = 64;          // rows per CTA
+constexpr int kDenseMaxSlices = 32;    // FP8 K <= 16384 -> 1024 blocks -> 32 slices
+
+struct DenseArgs {
+    const __nv_bfloat16* x;
+    const uint8_t* w;
+    const uint8_t* s;
+    int K, N;
+    long long w_stride, s_stride;      // bytes per row of W / per row of the scale tensor
+    __nv_bfloat16* y;
+};
+
+// Where the scale of (row, block) lives, how it is fetched (raw 32 bits) and what it is worth.
+struct Fp4Scale {   // E8M0 [N, K/32]: one byte per row per block
+    __device__ static __forceinline__ uint32_t fetch(const uint8_t* s, int row, int blk, long long s_stride) {
+        return ldg_stream_u8(s + (long long)row * s_stride + blk);
+    }
+    __device__ static __forceinline__ float value(uint32_t raw) { return e8m0_to_float(raw); }
+};
+struct Fp8Scale {   // E8M0 [N/128, K/128]: one byte per 128x128 tile; a block is 16 elements
+    __device__ static __forceinline__ uint32_t fetch(const uint8_t* s, int row, int blk, long long s_stride) {
+        return ldg_stream_u8(s + (long long)(row >> 7) * s_stride + (blk >> 3));
+    }
+    __device__ static __forceinline__ float value(uint32_t raw) { return e8m0_to_float(raw); }
+};
+struct Fp8ScaleF32 {   // FP32 [N/128, K/128], row stride in bytes
+    __device__ static __forceinline__ uint32_t fetch(const uint8_t* s, int row, int blk, long long s_stride) {
+        return __ldg(reinterpret_cast<const uint32_t*>(s + (long long)(row >> 7) * s_stride) + (blk >> 3));
+    }
+    __device__ static __forceinline__ float value(uint32_t raw) { return __uint_as_float(raw); }
+};
+
+struct DenseBatch {
+    uint4 w[kDenseRows];
+    uint32_t s[kDenseRows];
+};
+
+template <class Sc>
+__device__ __forceinline__ void dense_issue(const DenseArgs& a, int row, int step, int row_end, int blk,
+                                            bool lane_ok, DenseBatch& b) {
+#pragma unroll
+    for (int i = 0; i < kDenseRows; ++i) {
+        const int n = row + i * step;
+        b.w[i] = make_uint4(0, 0, 0, 0);
+        b.s[i] = 0;
+        if (n < row_end && lane_ok) {
+            b.w[i] = ldg_stream_v4(a.w + (long long)n * a.w_stride + (long long)blk * 16);
+            b.s[i] = Sc::fetch(a.s, n, blk, a.s_stride);
+        }
+    }
+}
+
+template <class Fmt, class Sc>
+__device__ __forceinline__ void dense_consume(const DenseBatch& b, const ActBlock<Fmt>& xb, int lane, int local0,
+                                              int step, int n_local, int ks, float (*part)[kDenseMaxSlices]) {
+    float v[kDenseRows];
+#pragma unroll
+    for (int i = 0; i < kDenseRows; ++i) {
+        v[i] = 0.f;
+        if (local0 + i * step < n_local) v[i] = Fmt::dot(b.w[i], xb.h) * (Sc::value(b.s[i]) * xb.scale);
+    }
+    multi_reduce<kDenseRows>(v, lane);
+    if (multi_reduce_owner<kDenseRows>(lane)) {
+        const int local = local0 + multi_reduce_index<kDenseRows>(lane) * step;
+        if (local < n_local) part[local][ks] = v[0];
+    }
+}
+
+template <class Fmt, class Sc>
+__global__ void __launch_bounds__(kDenseThreads, 2) dense_gemv_kernel(const DenseArgs a) {
+    __shared__ float part[kDenseCap][kDenseMaxSlices];
+    pdl_launch_dependents();
+
+    const int lane = threadIdx.x & 31;
+    const int warp = threadIdx.x >> 5;
+    const int n_warps = blockDim.x >> 5;
+    const int n_blk = a.K / Fmt::kElems;
+    const int n_slices = (n_blk + 31) >> 5;
+    const int n_groups = max(1, n_warps / n_slices);
+    const int n_tasks = n_slices * n_groups;
+
+    const int r_begin = (int)((long long)a.N * blockIdx.x / gridDim.x);
+    const int r_end = (int)((long long)a.N * (blockIdx.x + 1) / gridDim.x);
+    const int n_local = r_end - r_begin;
+    const int span = kDenseRows * n_groups;
+
+    bool waited = false;
+    for (int task = warp; task < n_tasks; task += n_warps) {
+        const int ks = task % n_slices;
+        const int rg = task / n_slices;
+        const int blk = ks * 32 + lane;
+        const bool lane_ok = blk < n_blk;
+
+        DenseBatch b0, b1;
+        // weights never depend on the previous kernel in the stream: request them before waiting for it
+        dense_issue<Sc>(a, r_begin + rg, n_groups, r_end, blk, lane_ok, b0);
+        if (!waited) { pdl_wait(); waited = true; }
+
+        ActBlock<Fmt> xb;
+        act_block_load_bf16<Fmt>(a.x + (size_t)blk * Fmt::kElems, lane_ok, xb);
+
+        for (int local0 = rg; local0 < n_local; local0 += 2 * span) {
+            dense_issue<Sc>(a, r_begin + local0 + span, n_groups, r_end, blk, lane_ok, b1);
+            dense_consume<Fmt, Sc>(b0, xb, lane, local0, n_groups, n_local, ks, part);
+            dense_issue<Sc>(a, r_begin + local0 + 2 * span, n_groups, r_end, blk, lane_ok, b0);
+            dense_consume<Fmt, Sc>(b1, xb, lane, local0 + span, n_groups, n_local, ks, part);
+        }
+    }
+    if (!waited) pdl_wait();
+    __syncthreads();
+
+    for (int t = threadIdx.x; t < n_local; t += blockDim.x) {
+        float acc = 0.f;
+        for (int s = 0; s < n_slices; ++s) acc += part[t][s];
+        a.y[r_begin + t] = __float2bfloat16(acc);
+    }
+}
+
+// Any alignment, any stride: one warp per row, byte loads, FP32 FMA.  Only taken when a base pointer
+// or a row stride is not a multiple of 16 bytes.
+template <class Fmt, class Sc>
+__global__ void dense_gemv_unaligned_kernel(const DenseArgs a) {
+    const int lane = threadIdx.x & 31;
+    const int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (row >= a.N) return;
+    const int n_blk = a.K / Fmt::kElems;
+    const uint8_t* wrow = a.w + (long long)row * a.w_stride;
+    float acc = 0.f;
+    for (int blk = lane; blk < n_blk; blk += 32) {
+        const float sc = Sc::value(Sc::fetch(a.s, row, blk, a.s_stride));
+        const __nv_bfloat16* xp = a.x + (size_t)blk * Fmt::kElems;
+        float part = 0.f;
+        for (int i = 0; i < 16; ++i) {
+            const uint32_t byte = wrow[(size_t)blk * 16 + i];
+            if (Fmt::kElems == 32) {
+                __half2 h[4];
+                e2m1x8_to_h2x4(byte, h);
+                const float2 f = __half22float2(h[0]);
+                part = fmaf(f.x, __bfloat162float(xp[2 * i]), part);
+                part = fmaf(f.y, __bfloat162float(xp[2 * i + 1]), part);
+            } else {
+                __half2 h[2];
+                e4m3x4_to_h2x2(byte, h);
+                part = fmaf(__low2float(h[0]), __bfloat162float(xp[i]), part);
+            }
+        }
+        acc = fmaf(part, sc, acc);
+    }
+    for (int off = 16; off > 0; off >>= 1) acc += __shfl_xor_sync(kFullMask, acc, off);
+    if (lane == 0) a.y[row] = __float2bfloat16(acc);
+}
+
+inline int dense_sm_count() {
+    static int cached[64] = {0};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 148;
+    if (cached[dev] == 0) {
+        int n = 0;
+        if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+        cached[dev] = n;
+    }
+    return cached[dev];
+}
+
+inline bool dense_pdl_enabled() {
+    static int v = -1;
+    if (v < 0) {
+        const char* e = std::getenv("DSV4_B200_PDL");
+        v = (e && e[0] == '0') ? 0 : 1;
+    }
+    return v == 1;
+}
+
+// Launches the aligned streaming kernel when it can, the byte-wise one otherwise.
+template <class Fmt, class Sc>
+inline cudaError_t dense_launch(const DenseArgs& a, cudaStream_t stream) {
+    auto mis = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) != 0; };
+    if (mis(a.x) || mis(a.w) || (a.w_stride & 15) != 0) {
+        const int warps = 8;
+        dense_gemv_unaligned_kernel<Fmt, Sc><<<(a.N + warps - 1) / warps, warps * 32, 0, stream>>>(a);
+        return cudaGetLastError();
+    }
+    long long grid = 2LL * dense_sm_count();
+    const long long need = ((long long)a.N + kDenseCap - 1) / kDenseCap;
+    if (grid < need) grid = need;
+    if (grid > a.N) grid = a.N;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)grid);
+    cfg.blockDim = dim3(kDenseThreads);
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = dense_pdl_enabled() ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, dense_gemv_kernel<Fmt, Sc>, a);
+}
+
+}  // namespace dsv4

@@ -1,0 +1,67 @@
+// libfp8_e4m3_gemv.so — FP8 E4M3 dense GEMV, M = 1, 128x128 block scales, for B200 (sm_100a).
+// Drop-in for the reference's kernel/fp8-dense/fp8_e4m3_gemv.cu:132-174 (same symbol, argument order and
+// return codes).  The kernel itself is in dense_gemv.cuh.
+#include "dense_gemv.cuh"
+
+using namespace dsv4;
+
+// y[n] = bf16(sum_k e4m3(W[n,k]) * 2^(S[n/128,k/128]-127) * x[k]); W_fp8 [N, K] raw E4M3 bytes,
+// W_scale [N/128, K/128] E8M0, row strides in bytes.
+// Returns 0, or -1 (K % 128), -2 (N % 128), -3 (K > 16384), -4 (launch failure) as the reference does;
+// added: -8 for a null pointer or negative sizes.  N == 0 is a no-op.
+DSV4_API int fp8_e4m3_gemv_m1(const __nv_bfloat16* x, const uint8_t* W_fp8, const uint8_t* W_scale, int K, int N,
+                              int64_t weight_row_stride_bytes, int64_t scale_row_stride_bytes, __nv_bfloat16* y,
+                              cudaStream_t stream) {
+    if (K <= 0 || K % 128 != 0) {
+        std::fprintf(stderr, "fp8_e4m3_gemv_m1: K=%d not a positive multiple of 128\n", K);
+        return -1;
+    }
+    if (N < 0 || N % 128 != 0) {
+        std::fprintf(stderr, "fp8_e4m3_gemv_m1: N=%d not a multiple of 128\n", N);
+        return -2;
+    }
+    if (K > 16384) {
+        std::fprintf(stderr, "fp8_e4m3_gemv_m1: K=%d > 16384\n", K);
+        return -3;
+    }
+    if (!x || !W_fp8 || !W_scale || !y) {
+        std::fprintf(stderr, "fp8_e4m3_gemv_m1: null pointer\n");
+        return -8;
+    }
+    if (N == 0) return 0;
+    DenseArgs a;
+    a.x = x; a.w = W_fp8; a.s = W_scale; a.K = K; a.N = N;
+    a.w_stride = weight_row_stride_bytes; a.s_stride = scale_row_stride_bytes; a.y = y;
+    const cudaError_t err = dense_launch<Fp8Format, Fp8Scale>(a, stream);
+    if (err != cudaSuccess) {
+        std::fprintf(stderr, "fp8_e4m3_gemv_m1 launch failed: %s\n", cudaGetErrorString(err));
+        return -4;
+    }
+    return 0;
+}
+
+// Additive: the same GEMV with FP32 block scales (scale = amax / 448 style checkpoints) instead of E8M0 bytes.
+// W_scale_f32 [N/128, K/128] FP32, its row stride in BYTES.  Same return codes as fp8_e4m3_gemv_m1, plus -8 when
+// the scale pointer or stride is not 4-byte aligned.
+DSV4_API int fp8_e4m3_gemv_m1_f32scale(const __nv_bfloat16* x, const uint8_t* W_fp8, const float* W_scale_f32, int K,
+                                       int N, int64_t weight_row_stride_bytes, int64_t scale_row_stride_bytes,
+                                       __nv_bfloat16* y, cudaStream_t stream) {
+    if (K <= 0 || K % 128 != 0) return -1;
+    if (N < 0 || N % 128 != 0) return -2;
+    if (K > 16384) return -3;
+    if (!x || !W_fp8 || !W_scale_f32 || !y || (reinterpret_cast<uintptr_t>(W_scale_f32) & 3u) ||
+        (scale_row_stride_bytes & 3)) {
+        std::fprintf(stderr, "fp8_e4m3_gemv_m1_f32scale: null pointer or misaligned FP32 scales\n");
+        return -8;
+    }
+    if (N == 0) return 0;
+    DenseArgs a;
+    a.x = x; a.w = W_fp8; a.s = reinterpret_cast<const uint8_t*>(W_scale_f32); a.K = K; a.N = N;
+    a.w_stride = weight_row_stride_bytes; a.s_stride = scale_row_stride_bytes; a.y = y;
+    const cudaError_t err = dense_launch<Fp8Format, Fp8ScaleF32>(a, stream);
+    if (err != cudaSuccess) {
+        std::fprintf(stderr, "fp8_e4m3_gemv_m1_f32scale launch failed: %s\n", cudaGetErrorString(err));
+        return -4;
+    }
+    return 0;
+}

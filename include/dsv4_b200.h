@@ -1,0 +1,91 @@
+/* C ABI of the B200 (sm_100a) quantized-weight GEMV libraries.
+ *
+ * Three shared objects carry the file names and symbols the reference's callers load
+ * (its ctypes bindings, and its C++ engine through dlsym / a global-namespace extern):
+ *
+ *   libmxfp4_grouped_gemv.so   mxfp4_grouped_gemv_topk, mxfp4_grouped_workspace_bytes
+ *   libmxfp4_gemv.so           mxfp4_gemv_m1
+ *   libfp8_e4m3_gemv.so        fp8_e4m3_gemv_m1
+ *
+ * Conventions, identical to the reference: every pointer is DEVICE memory owned by the caller; nothing is
+ * allocated, freed or retained; work is enqueued on `stream` and the call returns without synchronising;
+ * the return value is 0 on success and negative on a rejected argument or a failed launch (message on stderr);
+ * outputs are fully overwritten; workspace contents are undefined afterwards.  The entry points are
+ * re-entrant; concurrent calls need distinct workspaces.  `stream` is a cudaStream_t passed as void*.
+ * bf16 values are passed as uint16_t bit patterns (= __nv_bfloat16).
+ *
+ * Alignment: x, the packed-weight bases and the workspace of the grouped entry must be 16-byte aligned
+ * (cudaMalloc and torch allocations are); the dense entries take any alignment and stride (a slower
+ * byte-wise kernel runs when a base or row stride is not a multiple of 16).
+ */
+#ifndef DSV4_B200_H
+#define DSV4_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* ---- libmxfp4_grouped_gemv.so ------------------------------------------------------------------------- */
+
+/* Replaces kernel/mxfp4-routed/mxfp4_grouped_gemv.cu:294-403.
+ * out[o] = bf16( sum_e rweights[e] * W2_e[o,:] . ( silu(W1_e x) * (W3_e x) ) ), e < n_exp, experts stacked:
+ * W1/W3 packed [n_exp, hidden, K_in/2], scale [n_exp, hidden, K_in/32]; W2 packed [n_exp, out_dim, hidden/2],
+ * scale [n_exp, out_dim, hidden/32].  Packed bytes hold two E2M1 values (low nibble = even index), scales are
+ * E8M0 bytes (2^(b-127); 0xFF contributes 0).
+ * Returns -1 K_in % 32, -2 hidden % 32, -3 K_in or hidden > 4096, -4 n_exp != 6, -5/-6 launch failure (as the
+ * reference), -8 null / misaligned pointer or out_dim <= 0. */
+int mxfp4_grouped_gemv_topk(const uint16_t* x, const uint8_t* W1_packed, const uint8_t* W3_packed,
+                            const uint8_t* W2_packed, const uint8_t* W1_scale, const uint8_t* W3_scale,
+                            const uint8_t* W2_scale, const float* rweights, int K_in, int hidden, int out_dim,
+                            int n_exp, uint16_t* out, void* workspace, void* stream);
+
+/* Replaces kernel/mxfp4-routed/mxfp4_grouped_gemv.cu:406-409.  Bytes the caller must provide as `workspace`. */
+size_t mxfp4_grouped_workspace_bytes(int n_exp, int hidden, int out_dim);
+
+/* Added (no counterpart; removes the gather of kernel/cpp-engine-mxfp4/routed.cu:266-283): the same FFN with the
+ * n_exp experts (1..8) picked by DEVICE index array `topk_ids` from bank tensors stacked over all experts. */
+int mxfp4_grouped_gemv_topk_ids(const uint16_t* x, const uint8_t* bank_W1_packed, const uint8_t* bank_W3_packed,
+                                const uint8_t* bank_W2_packed, const uint8_t* bank_W1_scale,
+                                const uint8_t* bank_W3_scale, const uint8_t* bank_W2_scale, const int* topk_ids,
+                                const float* rweights, int K_in, int hidden, int out_dim, int n_exp, uint16_t* out,
+                                void* workspace, void* stream);
+
+/* Added (replaces the host round trip of kernel/cpp-engine-mxfp4/routed.cu:156-208): router scores, top-k and
+ * weights on the device.  logits FP32 [n_tokens, n_experts]; score_func 0 = softmax renormalised over the picks,
+ * 1 = sqrt(softplus), w = s / (sum s + eps) * scaling; ids_out int32 [n_tokens, k] by descending score, ties to the
+ * lowest index; w_out FP32 [n_tokens, k].  Returns -1 bad shape, -2 null pointer, -3 launch failure. */
+int mxfp4_moe_route_topk(const float* logits, int n_tokens, int n_experts, int k, int score_func, float eps,
+                         float scaling, int* ids_out, float* w_out, void* stream);
+
+/* Added (diagnostic; semantics of runtime/mxfp4_loader.py:272-309, scale 0xFF -> NaN): MXFP4 -> bf16 [rows, cols]. */
+int mxfp4_dequant_bf16(const uint8_t* packed, const uint8_t* scale, long long rows, int cols, uint16_t* out,
+                       void* stream);
+
+/* ---- libmxfp4_gemv.so --------------------------------------------------------------------------------- */
+
+/* Replaces kernel/mxfp4-dense/mxfp4_gemv.cu:131-166.  y[n] = bf16(sum_k W[n,k] x[k]); W_packed [N, K/2],
+ * W_scale [N, K/32], row strides in bytes.  Returns -1 K % 32, -2 K > 8192, -3 launch failure (as the reference),
+ * -8 null pointer or N < 0. */
+int mxfp4_gemv_m1(const uint16_t* x, const uint8_t* W_packed, const uint8_t* W_scale, int K, int N,
+                  int64_t packed_row_stride_bytes, int64_t scale_row_stride_bytes, uint16_t* y, void* stream);
+
+/* ---- libfp8_e4m3_gemv.so ------------------------------------------------------------------------------ */
+
+/* Replaces kernel/fp8-dense/fp8_e4m3_gemv.cu:132-174.  y[n] = bf16(sum_k e4m3(W[n,k]) 2^(S[n/128,k/128]-127) x[k]);
+ * W_fp8 [N, K] raw E4M3, W_scale [N/128, K/128] E8M0, row strides in bytes.  Returns -1 K % 128, -2 N % 128,
+ * -3 K > 16384, -4 launch failure (as the reference), -8 null pointer. */
+int fp8_e4m3_gemv_m1(const uint16_t* x, const uint8_t* W_fp8, const uint8_t* W_scale, int K, int N,
+                     int64_t weight_row_stride_bytes, int64_t scale_row_stride_bytes, uint16_t* y, void* stream);
+
+/* Added: the same with FP32 tile scales [N/128, K/128] (row stride in bytes). */
+int fp8_e4m3_gemv_m1_f32scale(const uint16_t* x, const uint8_t* W_fp8, const float* W_scale_f32, int K, int N,
+                              int64_t weight_row_stride_bytes, int64_t scale_row_stride_bytes, uint16_t* y,
+                              void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* DSV4_B200_H */
