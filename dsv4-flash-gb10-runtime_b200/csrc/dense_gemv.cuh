@@ -150,15 +150,11 @@ __global__ void dense_gemv_unaligned_kernel(const DenseArgs a) {
         for (int i = 0; i < 16; ++i) {
             const uint32_t byte = wrow[(size_t)blk * 16 + i];
             if (Fmt::kElems == 32) {
-                __half2 h[4];
-                e2m1x8_to_h2x4(byte, h);
-                const float2 f = __half22float2(h[0]);
+                const float2 f = e2m1x2_to_float2(byte);
                 part = fmaf(f.x, __bfloat162float(xp[2 * i]), part);
                 part = fmaf(f.y, __bfloat162float(xp[2 * i + 1]), part);
             } else {
-                __half2 h[2];
-                e4m3x4_to_h2x2(byte, h);
-                part = fmaf(__low2float(h[0]), __bfloat162float(xp[i]), part);
+                part = fmaf(e4m3_to_float(byte), __bfloat162float(xp[i]), part);
             }
         }
         acc = fmaf(part, sc, acc);

@@ -24,11 +24,11 @@ DSV4_API int fp8_e4m3_gemv_m1(const __nv_bfloat16* x, const uint8_t* W_fp8, cons
         std::fprintf(stderr, "fp8_e4m3_gemv_m1: K=%d > 16384\n", K);
         return -3;
     }
+    if (N == 0) return 0;
     if (!x || !W_fp8 || !W_scale || !y) {
         std::fprintf(stderr, "fp8_e4m3_gemv_m1: null pointer\n");
         return -8;
     }
-    if (N == 0) return 0;
     DenseArgs a;
     a.x = x; a.w = W_fp8; a.s = W_scale; a.K = K; a.N = N;
     a.w_stride = weight_row_stride_bytes; a.s_stride = scale_row_stride_bytes; a.y = y;

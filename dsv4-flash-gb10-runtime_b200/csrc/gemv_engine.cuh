@@ -18,6 +18,8 @@
 #include <cuda_runtime.h>
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
+#include <cuda_fp4.h>
+#include <cuda_fp8.h>
 #include <cstdint>
 
 #define DSV4_API extern "C" __attribute__((visibility("default")))
@@ -91,6 +93,18 @@ __device__ __forceinline__ void e2m1x8_to_h2x4(uint32_t w, __half2 (&h)[4]) {
     h[1] = *reinterpret_cast<__half2*>(&r1);
     h[2] = *reinterpret_cast<__half2*>(&r2);
     h[3] = *reinterpret_cast<__half2*>(&r3);
+}
+
+// One byte = two E2M1 nibbles -> (low nibble, high nibble) as floats; for the byte-at-a-time paths.
+__device__ __forceinline__ float2 e2m1x2_to_float2(uint32_t byte) {
+    const __half2_raw raw = __nv_cvt_fp4x2_to_halfraw2((__nv_fp4x2_storage_t)(byte & 0xffu), __NV_E2M1);
+    return __half22float2(*reinterpret_cast<const __half2*>(&raw));
+}
+
+// One E4M3 byte -> float.
+__device__ __forceinline__ float e4m3_to_float(uint32_t byte) {
+    const __half_raw raw = __nv_cvt_fp8_to_halfraw((__nv_fp8_storage_t)(byte & 0xffu), __NV_E4M3);
+    return __half2float(*reinterpret_cast<const __half*>(&raw));
 }
 
 // Four E4M3 bytes -> two fp16x2 (exact: E4M3 is a subset of fp16).
@@ -208,6 +222,76 @@ __device__ __forceinline__ void act_block_load_f32(const float* src, bool valid,
         v[4 * i + 0] = q.x; v[4 * i + 1] = q.y; v[4 * i + 2] = q.z; v[4 * i + 3] = q.w;
     }
     act_block_finish<Fmt>(v, a);
+}
+
+// ---------------------------------------------------------------------------------------------
+// lane-resident activations for a whole row: BPL blocks per lane, block j of the lane is block
+// (lane + 32 j) of the vector, so that load j of a warp covers 512 contiguous bytes of a weight row
+// ---------------------------------------------------------------------------------------------
+
+template <class Fmt, int BPL>
+struct LaneAct {
+    __half2 h[BPL][Fmt::kPairs];   // activations times 1/scale, as fp16x2
+    float scale;                   // one power of two for all the lane's blocks
+};
+
+__device__ __forceinline__ void load8_as_float(const __nv_bfloat16* p, float (&v)[8]) {
+    const uint4 q = __ldcg(reinterpret_cast<const uint4*>(p));
+    const uint32_t u[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        v[2 * j + 0] = __uint_as_float(u[j] << 16);
+        v[2 * j + 1] = __uint_as_float(u[j] & 0xffff0000u);
+    }
+}
+
+__device__ __forceinline__ void load8_as_float(const float* p, float (&v)[8]) {
+    const float4 a = __ldcg(reinterpret_cast<const float4*>(p));
+    const float4 b = __ldcg(reinterpret_cast<const float4*>(p) + 1);
+    v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+}
+
+// Elem is __nv_bfloat16 (the caller's activation vector) or float (the SwiGLU intermediate).
+// Two passes over the lane's elements (largest magnitude, then convert) keep the register need small;
+// the vector is at most 16 KB and sits in L2.
+template <class Fmt, int BPL, class Elem>
+__device__ __forceinline__ void lane_act_load(const Elem* x, int lane, int n_blk, LaneAct<Fmt, BPL>& a) {
+    uint32_t amax_bits = 0;
+#pragma unroll
+    for (int j = 0; j < BPL; ++j) {
+        const int blk = lane + 32 * j;
+        if (blk < n_blk) {
+#pragma unroll
+            for (int c = 0; c < Fmt::kElems / 8; ++c) {
+                float v[8];
+                load8_as_float(x + (size_t)blk * Fmt::kElems + 8 * c, v);
+#pragma unroll
+                for (int i = 0; i < 8; ++i) amax_bits = max(amax_bits, __float_as_uint(v[i]) & 0x7fffffffu);
+            }
+        }
+    }
+    int e = (int)(amax_bits >> 23) - Fmt::kActExp;   // biased exponent of the scale
+    e = min(max(e, 1), 253);
+    a.scale = __uint_as_float((uint32_t)e << 23);
+    const float inv = __uint_as_float((uint32_t)(254 - e) << 23);
+#pragma unroll
+    for (int j = 0; j < BPL; ++j) {
+        const int blk = lane + 32 * j;
+#pragma unroll
+        for (int c = 0; c < Fmt::kElems / 8; ++c) {
+            float v[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+            if (blk < n_blk) load8_as_float(x + (size_t)blk * Fmt::kElems + 8 * c, v);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) a.h[j][4 * c + i] = __floats2half2_rn(v[2 * i] * inv, v[2 * i + 1] * inv);
+        }
+    }
+}
+
+// E8M0 byte -> float for the GEMV hot path: 0xFF contributes 0 (as in the kernels this library replaces);
+// byte 0 gives 0 instead of 2^-127, a value no product with a bf16 activation can lift above 1e-36.
+__device__ __forceinline__ float e8m0_to_float_fast(uint32_t b) {
+    const uint32_t bits = b << 23;
+    return __uint_as_float(b == 255u ? 0u : bits);
 }
 
 // ---------------------------------------------------------------------------------------------

@@ -20,11 +20,11 @@ DSV4_API int mxfp4_gemv_m1(const __nv_bfloat16* x, const uint8_t* W_packed, cons
         std::fprintf(stderr, "mxfp4_gemv_m1: K=%d > 8192\n", K);
         return -2;
     }
+    if (N == 0) return 0;
     if (N < 0 || !x || !W_packed || !W_scale || !y) {
         std::fprintf(stderr, "mxfp4_gemv_m1: null pointer or N=%d < 0\n", N);
         return -8;
     }
-    if (N == 0) return 0;
     DenseArgs a;
     a.x = x; a.w = W_packed; a.s = W_scale; a.K = K; a.N = N;
     a.w_stride = packed_row_stride_bytes; a.s_stride = scale_row_stride_bytes; a.y = y;

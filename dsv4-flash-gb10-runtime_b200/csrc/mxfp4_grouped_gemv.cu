@@ -7,255 +7,236 @@
 // order, return codes and ownership rules (caller owns all buffers, work is enqueued on the caller's
 // stream, no allocation, no synchronisation).
 //
-// Two kernels, chained by programmatic dependent launch so that the second one is already resident
-// and has its first weight tiles in flight while the first one drains:
-//   gate/up kernel : every CTA owns a contiguous range of (expert, hidden-row) pairs; a warp owns a
-//                    1024-element slice of the reduction axis and walks down the CTA's rows, W1 and W3
-//                    row of a pair together; per-slice partial sums meet in shared memory, the CTA then
-//                    writes silu(g)*u as FP32 into the workspace.
-//   down kernel    : every CTA owns a contiguous range of output rows for ALL experts; a warp owns
-//                    (expert, 1024-slice); the router-weighted sum over experts is taken inside the CTA
-//                    in a fixed order (deterministic, no float atomics), rounded once to bf16.
+// Two kernels, chained by programmatic dependent launch so that the second one can request its first
+// weight rows while the first one drains:
+//   gate/up kernel : a warp owns a contiguous run of (expert, hidden-row) pairs and streams the W1 and W3
+//                    row of a pair whole (a lane owns up to 4 blocks of the row, the activation vector
+//                    lives in its registers), reduces across lanes and writes silu(g)*u as FP32 into the
+//                    workspace; no shared memory, no block barrier.
+//   down kernel    : a CTA owns a contiguous range of output rows for ALL experts, a warp owns one expert;
+//                    the router-weighted sum over experts is taken inside the CTA in a fixed order
+//                    (deterministic, no float atomics) and rounded once to bf16.
 #include "gemv_engine.cuh"
+#include "stream_ring.cuh"
+#include "grouped_args.cuh"
+#include "grouped_ring.cuh"
 
 #include <cstdio>
 #include <cstdlib>
 
 namespace dsv4 {
 
-constexpr int kMaxSlices = 4;        // reduction axis <= 4096 elements = 4 slices of 32 blocks
-constexpr int kMaxExperts = 8;       // experts per call (the reference fixes 6)
+constexpr int kMaxBlocksPerLane = 4;   // reduction axis <= 4096 elements = 128 blocks = 4 per lane
+constexpr int kMaxExperts = 8;         // experts per call (the reference fixes 6)
 
-constexpr int kGateThreads = 256;    // 8 warps
-constexpr int kGatePairs = 4;        // (W1,W3) row pairs per warp batch -> 8 x 16 B loads per lane in flight
-constexpr int kGateCap = 256;        // pairs per CTA held in shared memory
+constexpr int kGateThreads = 384;      // 12 warps, one (W1,W3) row pair in flight per warp
+constexpr int kDownThreads = 384;      // 12 warps = 6 experts x 2 row groups at the DSv4 shape
+constexpr int kDownCap = 64;           // output rows per CTA held in shared memory
+constexpr int kDownLoads = 8;          // 16-byte loads per lane per batch
 
-constexpr int kDownThreads = 384;    // 12 warps = 6 experts x 2 slices at the DSv4 shape
-constexpr int kDownRows = 8;         // rows per warp batch
-constexpr int kDownCap = 64;         // output rows per CTA
-constexpr int kDownMaxUnits = kMaxExperts * kMaxSlices;
 
-struct GroupedArgs {
-    const __nv_bfloat16* x;
-    const uint8_t* w1p; const uint8_t* w3p; const uint8_t* w2p;
-    const uint8_t* w1s; const uint8_t* w3s; const uint8_t* w2s;
-    const float* r;
-    const int* ids;                  // nullptr: expert slot e uses bank entry e (stacked weights)
-    int K, H, O, E;
-    long long strideAp, strideAs, strideBp, strideBs;   // bytes per expert
-    float* mid;                      // [E, H] FP32 SwiGLU intermediate (workspace)
-    __nv_bfloat16* out;
+// One weight row as seen by a lane: BPL 16-byte blocks and their scale bytes.
+template <int BPL>
+struct RowRegs {
+    uint4 w[BPL];
+    uint32_t s[BPL];
 };
 
-// ------------------------------------------------------------------------------------------------
-// gate/up + SwiGLU
-// ------------------------------------------------------------------------------------------------
-
-struct GateBatch {
-    uint4 w1[kGatePairs];
-    uint4 w3[kGatePairs];
-    uint32_t s1[kGatePairs];
-    uint32_t s3[kGatePairs];
-};
-
-struct PairCursor {      // next (expert slot, hidden row) this warp will request
-    int q, e, h;
-};
-
-__device__ __forceinline__ void gate_issue(const GroupedArgs& a, PairCursor& c, int step, int q_end,
-                                           int blk, bool lane_ok, GateBatch& b) {
+template <int BPL>
+__device__ __forceinline__ void row_clear(RowRegs<BPL>& r) {
 #pragma unroll
-    for (int i = 0; i < kGatePairs; ++i) {
-        b.w1[i] = make_uint4(0, 0, 0, 0);
-        b.w3[i] = make_uint4(0, 0, 0, 0);
-        b.s1[i] = 0;
-        b.s3[i] = 0;
-        if (c.q < q_end && lane_ok) {
-            const long long eid = a.ids ? a.ids[c.e] : c.e;
-            const long long po = eid * a.strideAp + (long long)c.h * (a.K >> 1) + (long long)blk * 16;
-            const long long so = eid * a.strideAs + (long long)c.h * (a.K >> 5) + blk;
-            b.w1[i] = ldg_stream_v4(a.w1p + po);
-            b.w3[i] = ldg_stream_v4(a.w3p + po);
-            b.s1[i] = ldg_stream_u8(a.w1s + so);
-            b.s3[i] = ldg_stream_u8(a.w3s + so);
+    for (int j = 0; j < BPL; ++j) { r.w[j] = make_uint4(0, 0, 0, 0); r.s[j] = 0; }
+}
+
+// wp / sp already point at this lane's first block / scale byte of the row.
+template <int BPL>
+__device__ __forceinline__ void row_issue(const uint8_t* wp, const uint8_t* sp, const bool (&ok)[BPL],
+                                          RowRegs<BPL>& r) {
+#pragma unroll
+    for (int j = 0; j < BPL; ++j)
+        if (ok[j]) {
+            r.w[j] = ldg_stream_v4(wp + 512 * j);
+            r.s[j] = ldg_stream_u8(sp + 32 * j);
         }
-        c.q += step;
-        c.h += step;
-        if (c.h >= a.H) { c.h -= a.H; c.e += 1; }
+}
+
+// Dot product of the lane's part of a row with the activations; each block's registers are refilled with the
+// same block of a later row (at nwp / nsp) as soon as they have been consumed, so the lane always has its
+// full set of loads in flight without a second register buffer.
+template <int BPL>
+__device__ __forceinline__ float row_dot_refill(RowRegs<BPL>& r, const LaneAct<Fp4Format, BPL>& a,
+                                                const uint8_t* nwp, const uint8_t* nsp, bool more,
+                                                const bool (&ok)[BPL]) {
+    float acc = 0.f;
+#pragma unroll
+    for (int j = 0; j < BPL; ++j) {
+        const float d = Fp4Format::dot(r.w[j], a.h[j]);
+        const float sc = e8m0_to_float_fast(r.s[j]);
+        if (more && ok[j]) {
+            r.w[j] = ldg_stream_v4(nwp + 512 * j);
+            r.s[j] = ldg_stream_u8(nsp + 32 * j);
+        }
+        acc = fmaf(d, sc, acc);
+    }
+    return acc * a.scale;
+}
+
+// ------------------------------------------------------------------------------------------------
+// gate/up + SwiGLU: a warp owns a contiguous run of (expert slot, hidden row) pairs and streams the W1 and
+// W3 row of a pair together (2 x BPL loads of 512 contiguous bytes per warp)
+// ------------------------------------------------------------------------------------------------
+
+struct GateCursor {
+    const uint8_t* w1; const uint8_t* w3; const uint8_t* s1; const uint8_t* s3;   // this lane's position in pair q
+    int q, h, e;
+};
+
+__device__ __forceinline__ void gate_seek(const GroupedArgs& a, GateCursor& c, int lane) {
+    const long long eid = a.ids ? (long long)a.ids[c.e] : (long long)c.e;
+    const long long po = eid * a.strideAp + (long long)c.h * (a.K >> 1) + lane * 16;
+    const long long so = eid * a.strideAs + (long long)c.h * (a.K >> 5) + lane;
+    c.w1 = a.w1p + po; c.w3 = a.w3p + po; c.s1 = a.w1s + so; c.s3 = a.w3s + so;
+}
+
+__device__ __forceinline__ void gate_advance(const GroupedArgs& a, GateCursor& c, int q_end, int lane) {
+    const int row_p = a.K >> 1, row_s = a.K >> 5;
+    c.q += 1;
+    c.h += 1;
+    c.w1 += row_p; c.w3 += row_p; c.s1 += row_s; c.s3 += row_s;
+    if (c.h == a.H) {          // next expert slot: stacked experts are contiguous, a bank needs a new base
+        c.h = 0;
+        c.e += 1;
+        if (a.ids != nullptr && c.q < q_end) gate_seek(a, c, lane);
     }
 }
 
-__device__ __forceinline__ void gate_consume(const GateBatch& b, const ActBlock<Fp4Format>& xb, int lane,
-                                             int local0, int step, int n_local, int ks,
-                                             float (*part)[kMaxSlices][2]) {
-    float v[2 * kGatePairs];
-#pragma unroll
-    for (int i = 0; i < kGatePairs; ++i) {
-        v[2 * i + 0] = 0.f;
-        v[2 * i + 1] = 0.f;
-        if (local0 + i * step < n_local) {   // warp-uniform: skip the arithmetic of rows past the range
-            v[2 * i + 0] = Fp4Format::dot(b.w1[i], xb.h) * (e8m0_to_float(b.s1[i]) * xb.scale);
-            v[2 * i + 1] = Fp4Format::dot(b.w3[i], xb.h) * (e8m0_to_float(b.s3[i]) * xb.scale);
-        }
-    }
-    multi_reduce<2 * kGatePairs>(v, lane);
-    if (multi_reduce_owner<2 * kGatePairs>(lane)) {
-        const int idx = multi_reduce_index<2 * kGatePairs>(lane);
-        const int local = local0 + (idx >> 1) * step;
-        if (local < n_local) part[local][ks][idx & 1] = v[0];
-    }
-}
-
-__global__ void __launch_bounds__(kGateThreads, 2) grouped_gate_up_kernel(const GroupedArgs a) {
-    __shared__ float part[kGateCap][kMaxSlices][2];
+template <int BPL>
+__global__ void __launch_bounds__(kGateThreads, 1) grouped_gate_up_kernel(const GroupedArgs a) {
     pdl_launch_dependents();
-
     const int lane = threadIdx.x & 31;
-    const int warp = threadIdx.x >> 5;
-    const int n_warps = blockDim.x >> 5;
+    const int gw = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    const int n_gw = gridDim.x * (blockDim.x >> 5);
     const int n_blk = a.K >> 5;
-    const int n_slices = (n_blk + 31) >> 5;
-    const int n_groups = n_warps / n_slices;          // host guarantees >= 1
-    const int ks = warp % n_slices;
-    const int rg = warp / n_slices;
-    const int blk = ks * 32 + lane;
-    const bool lane_ok = blk < n_blk;
-    const bool warp_ok = rg < n_groups;
+    bool ok[BPL];
+#pragma unroll
+    for (int j = 0; j < BPL; ++j) ok[j] = lane + 32 * j < n_blk;
 
     const long long total = (long long)a.E * a.H;
-    const int q_begin = (int)(total * blockIdx.x / gridDim.x);
-    const int q_end = (int)(total * (blockIdx.x + 1) / gridDim.x);
-    const int n_local = q_end - q_begin;
+    const int q_begin = (int)(total * gw / n_gw);
+    const int q_end = (int)(total * (gw + 1) / n_gw);
 
-    if (warp_ok) {
-        PairCursor cur;
-        cur.q = q_begin + rg;
-        cur.e = cur.q / a.H;
-        cur.h = cur.q - cur.e * a.H;
+    GateCursor cur;
+    cur.q = q_begin;
+    cur.e = q_begin / a.H;
+    cur.h = q_begin - cur.e * a.H;
+    cur.w1 = cur.w3 = cur.s1 = cur.s3 = nullptr;
 
-        GateBatch b0, b1;
-        // stacked weights do not depend on the previous kernel: request them before waiting for it
-        if (a.ids == nullptr) gate_issue(a, cur, n_groups, q_end, blk, lane_ok, b0);
-        pdl_wait();
-        if (a.ids != nullptr) gate_issue(a, cur, n_groups, q_end, blk, lane_ok, b0);
-
-        ActBlock<Fp4Format> xb;
-        act_block_load_bf16<Fp4Format>(a.x + (size_t)blk * 32, lane_ok, xb);
-
-        const int batch_span = kGatePairs * n_groups;
-        for (int local0 = rg; local0 < n_local; local0 += 2 * batch_span) {
-            gate_issue(a, cur, n_groups, q_end, blk, lane_ok, b1);
-            gate_consume(b0, xb, lane, local0, n_groups, n_local, ks, part);
-            gate_issue(a, cur, n_groups, q_end, blk, lane_ok, b0);
-            gate_consume(b1, xb, lane, local0 + batch_span, n_groups, n_local, ks, part);
-        }
-    } else {
-        pdl_wait();
+    RowRegs<BPL> g, u;
+    row_clear(g);
+    row_clear(u);
+    const bool any = q_begin < q_end;
+    // stacked weights do not depend on the previous kernel in the stream: request them before waiting for it
+    if (a.ids == nullptr && any) {
+        gate_seek(a, cur, lane);
+        row_issue<BPL>(cur.w1, cur.s1, ok, g);
+        row_issue<BPL>(cur.w3, cur.s3, ok, u);
     }
-    __syncthreads();
+    pdl_wait();
+    if (a.ids != nullptr && any) {
+        gate_seek(a, cur, lane);
+        row_issue<BPL>(cur.w1, cur.s1, ok, g);
+        row_issue<BPL>(cur.w3, cur.s3, ok, u);
+    }
+    LaneAct<Fp4Format, BPL> x;
+    lane_act_load<Fp4Format, BPL>(a.x, lane, n_blk, x);
 
-    for (int t = threadIdx.x; t < n_local; t += blockDim.x) {
-        float g = 0.f, u = 0.f;
-        for (int s = 0; s < n_slices; ++s) { g += part[t][s][0]; u += part[t][s][1]; }
-        a.mid[q_begin + t] = (g / (1.0f + __expf(-g))) * u;
+    for (int q = q_begin; q < q_end; ++q) {
+        gate_advance(a, cur, q_end, lane);                       // cur now describes pair q + 1
+        const bool more = q + 1 < q_end;
+        float v[2];
+        v[0] = row_dot_refill<BPL>(g, x, cur.w1, cur.s1, more, ok);
+        v[1] = row_dot_refill<BPL>(u, x, cur.w3, cur.s3, more, ok);
+        multi_reduce<2>(v, lane);                                // lane 0: gate sum, lane 16: up sum
+        const float up = __shfl_sync(kFullMask, v[0], 16);
+        if (lane == 0) a.mid[q] = (v[0] / (1.0f + __expf(-v[0]))) * up;
     }
 }
 
 // ------------------------------------------------------------------------------------------------
-// down projection + router-weighted combine
+// down projection + router-weighted combine: a CTA owns a contiguous range of output rows for ALL experts,
+// a warp owns (expert slot, row group); the sum over experts is taken in a fixed order inside the CTA
 // ------------------------------------------------------------------------------------------------
 
-struct DownBatch {
-    uint4 w[kDownRows];
-    uint32_t s[kDownRows];
-};
-
-__device__ __forceinline__ void down_issue(const GroupedArgs& a, long long eid, int row, int step, int row_end,
-                                           int blk, bool lane_ok, DownBatch& b) {
-#pragma unroll
-    for (int i = 0; i < kDownRows; ++i) {
-        const int o = row + i * step;
-        b.w[i] = make_uint4(0, 0, 0, 0);
-        b.s[i] = 0;
-        if (o < row_end && lane_ok) {
-            b.w[i] = ldg_stream_v4(a.w2p + eid * a.strideBp + (long long)o * (a.H >> 1) + (long long)blk * 16);
-            b.s[i] = ldg_stream_u8(a.w2s + eid * a.strideBs + (long long)o * (a.H >> 5) + blk);
-        }
-    }
-}
-
-__device__ __forceinline__ void down_consume(const DownBatch& b, const ActBlock<Fp4Format>& mb, int lane,
-                                             int local0, int step, int n_local, int unit,
-                                             float (*part)[kDownMaxUnits]) {
-    float v[kDownRows];
-#pragma unroll
-    for (int i = 0; i < kDownRows; ++i) {
-        v[i] = 0.f;
-        if (local0 + i * step < n_local)
-            v[i] = Fp4Format::dot(b.w[i], mb.h) * (e8m0_to_float(b.s[i]) * mb.scale);
-    }
-    multi_reduce<kDownRows>(v, lane);
-    if (multi_reduce_owner<kDownRows>(lane)) {
-        const int local = local0 + multi_reduce_index<kDownRows>(lane) * step;
-        if (local < n_local) part[local][unit] = v[0];
-    }
-}
-
+template <int BPL>
 __global__ void __launch_bounds__(kDownThreads, 1) grouped_down_kernel(const GroupedArgs a) {
-    __shared__ float part[kDownCap][kDownMaxUnits];
+    constexpr int RB = kDownLoads / BPL;          // rows in flight per warp
+    __shared__ float part[kDownCap][kMaxExperts];
     pdl_launch_dependents();
 
     const int lane = threadIdx.x & 31;
     const int warp = threadIdx.x >> 5;
     const int n_warps = blockDim.x >> 5;
     const int n_blk = a.H >> 5;
-    const int n_slices = (n_blk + 31) >> 5;
-    const int n_units = a.E * n_slices;                       // (expert, slice)
-    const int n_groups = max(1, n_warps / n_units);           // row groups sharing a unit
-    const int n_tasks = n_units * n_groups;
+    bool ok[BPL];
+#pragma unroll
+    for (int j = 0; j < BPL; ++j) ok[j] = lane + 32 * j < n_blk;
 
+    const int n_groups = n_warps / a.E;                       // host guarantees E <= n_warps
+    const int e = warp % a.E;
+    const int rg = warp / a.E;
     const int o_begin = (int)((long long)a.O * blockIdx.x / gridDim.x);
     const int o_end = (int)((long long)a.O * (blockIdx.x + 1) / gridDim.x);
     const int n_local = o_end - o_begin;
+    // this warp's rows: a contiguous share of the CTA's range
+    const int l_begin = (int)((long long)n_local * rg / n_groups);
+    const int l_end = (rg < n_groups) ? (int)((long long)n_local * (rg + 1) / n_groups) : l_begin;
+    const int row_p = a.H >> 1, row_s = a.H >> 5;
+    const bool any = l_begin < l_end;
 
-    bool waited = false;
-    for (int task = warp; task < n_tasks; task += n_warps) {
-        const int unit = task % n_units;
-        const int rg = task / n_units;
-        const int e = unit / n_slices;
-        const int ks = unit - e * n_slices;
-        const int blk = ks * 32 + lane;
-        const bool lane_ok = blk < n_blk;
-        const int span = kDownRows * n_groups;
+    RowRegs<BPL> b[RB];
+#pragma unroll
+    for (int i = 0; i < RB; ++i) row_clear(b[i]);
 
-        DownBatch b0, b1;
-        long long eid = e;
-        if (!waited && a.ids == nullptr) down_issue(a, eid, o_begin + rg, n_groups, o_end, blk, lane_ok, b0);
-        if (!waited) pdl_wait();
-        if (a.ids != nullptr) eid = a.ids[e];
-        if (waited || a.ids != nullptr) down_issue(a, eid, o_begin + rg, n_groups, o_end, blk, lane_ok, b0);
-        waited = true;
+    const uint8_t* wp = nullptr;     // this lane's position in row l0 of the loop below
+    const uint8_t* sp = nullptr;
+    auto first_issue = [&]() {
+        const long long eid = a.ids ? (long long)a.ids[e] : (long long)e;
+        wp = a.w2p + eid * a.strideBp + (long long)(o_begin + l_begin) * row_p + lane * 16;
+        sp = a.w2s + eid * a.strideBs + (long long)(o_begin + l_begin) * row_s + lane;
+#pragma unroll
+        for (int i = 0; i < RB; ++i)
+            if (l_begin + i < l_end) row_issue<BPL>(wp + (long long)i * row_p, sp + i * row_s, ok, b[i]);
+    };
+    if (a.ids == nullptr && any) first_issue();
+    pdl_wait();
+    if (a.ids != nullptr && any) first_issue();
 
-        ActBlock<Fp4Format> mb;
-        act_block_load_f32<Fp4Format>(a.mid + (size_t)e * a.H + (size_t)blk * 32, lane_ok, mb);
-
-        for (int local0 = rg; local0 < n_local; local0 += 2 * span) {
-            down_issue(a, eid, o_begin + local0 + span, n_groups, o_end, blk, lane_ok, b1);
-            down_consume(b0, mb, lane, local0, n_groups, n_local, unit, part);
-            down_issue(a, eid, o_begin + local0 + 2 * span, n_groups, o_end, blk, lane_ok, b0);
-            down_consume(b1, mb, lane, local0 + span, n_groups, n_local, unit, part);
+    if (any) {
+        LaneAct<Fp4Format, BPL> m;
+        lane_act_load<Fp4Format, BPL>(a.mid + (size_t)e * a.H, lane, n_blk, m);
+        for (int l0 = l_begin; l0 < l_end; l0 += RB) {
+            float v[RB];
+#pragma unroll
+            for (int i = 0; i < RB; ++i) {
+                v[i] = 0.f;
+                if (l0 + i < l_end)
+                    v[i] = row_dot_refill<BPL>(b[i], m, wp + (long long)(RB + i) * row_p, sp + (RB + i) * row_s,
+                                               l0 + RB + i < l_end, ok);
+            }
+            multi_reduce<RB>(v, lane);
+            if (multi_reduce_owner<RB>(lane)) {
+                const int l = l0 + multi_reduce_index<RB>(lane);
+                if (l < l_end) part[l][e] = v[0];
+            }
+            wp += (long long)RB * row_p;
+            sp += RB * row_s;
         }
     }
-    if (!waited) pdl_wait();
     __syncthreads();
 
     for (int t = threadIdx.x; t < n_local; t += blockDim.x) {
         float acc = 0.f;
-        for (int e = 0; e < a.E; ++e) {
-            float y = 0.f;
-            for (int s = 0; s < n_slices; ++s) y += part[t][e * n_slices + s];
-            acc = fmaf(__ldcg(a.r + e), y, acc);
-        }
+        for (int k = 0; k < a.E; ++k) acc = fmaf(__ldcg(a.r + k), part[t][k], acc);
         a.out[o_begin + t] = __float2bfloat16(acc);
     }
 }
@@ -353,10 +334,7 @@ __global__ void dequant_bf16_kernel(const uint8_t* __restrict__ packed, const ui
         const uint8_t* src = packed + b * 16;
         __nv_bfloat16* dst = out + b * 32;
         for (int i = 0; i < 16; ++i) {
-            const uint32_t byte = src[i];
-            __half2 h[4];
-            e2m1x8_to_h2x4(byte, h);
-            const float2 f = __half22float2(h[0]);
+            const float2 f = e2m1x2_to_float2(src[i]);
             dst[2 * i + 0] = __float2bfloat16(f.x * sc);
             dst[2 * i + 1] = __float2bfloat16(f.y * sc);
         }
@@ -389,12 +367,12 @@ static bool pdl_enabled() {
 }
 
 template <class... Params, class... Args>
-static cudaError_t launch(void (*kernel)(Params...), dim3 grid, dim3 block, cudaStream_t stream, bool pdl,
-                          Args&&... args) {
+static cudaError_t launch_smem(void (*kernel)(Params...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                               bool pdl, Args&&... args) {
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = grid;
     cfg.blockDim = block;
-    cfg.dynamicSmemBytes = 0;
+    cfg.dynamicSmemBytes = smem;
     cfg.stream = stream;
     cudaLaunchAttribute attr[1];
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
@@ -404,16 +382,93 @@ static cudaError_t launch(void (*kernel)(Params...), dim3 grid, dim3 block, cuda
     return cudaLaunchKernelEx(&cfg, kernel, std::forward<Args>(args)...);
 }
 
-static int grouped_forward(const GroupedArgs& a, cudaStream_t stream, const char* who) {
+template <class... Params, class... Args>
+static cudaError_t launch(void (*kernel)(Params...), dim3 grid, dim3 block, cudaStream_t stream, bool pdl,
+                          Args&&... args) {
+    return launch_smem(kernel, grid, block, 0, stream, pdl, std::forward<Args>(args)...);
+}
+
+static bool ring_enabled() {
+    static int v = -1;
+    if (v < 0) {
+        const char* e = std::getenv("DSV4_B200_RING");
+        v = (e && e[0] == '0') ? 0 : 1;
+    }
+    return v == 1;
+}
+
+// Shared-memory opt-in above 48 KB is a per-function, per-device attribute: set it once per device.
+template <class Kernel>
+static cudaError_t allow_smem(Kernel kernel, size_t bytes, int (&done)[64]) {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) dev = 0;
+    if (done[dev] >= (int)bytes) return cudaSuccess;
+    cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
+    if (err == cudaSuccess) done[dev] = (int)bytes;
+    return err;
+}
+
+// Shared-memory ring path (grouped_ring.cuh).  Returns 1 when the shape is not one it serves.
+template <int KT, int HT>
+static int grouped_launch_ring(const GroupedArgs& a, cudaStream_t stream, const char* who, int h_shift) {
+    static int gate_done[64] = {0}, down_done[64] = {0};
+    const int sms = sm_count();
+    const bool pdl = pdl_enabled();
+    {
+        auto kernel = gate_up_ring_kernel<KT>;
+        cudaError_t err = allow_smem(kernel, GateRingLayout<KT>::kBytes, gate_done);
+        const long long pairs = (long long)a.E * a.H;
+        const long long grid = sms < pairs ? sms : pairs;
+        if (err == cudaSuccess)
+            err = launch_smem(kernel, dim3((unsigned)grid), dim3(kRingGateWarps * 32), GateRingLayout<KT>::kBytes,
+                              stream, pdl, a, h_shift);
+        if (err != cudaSuccess) {
+            std::fprintf(stderr, "%s: gate/up launch failed: %s\n", who, cudaGetErrorString(err));
+            return -5;
+        }
+    }
+    {
+        auto kernel = down_ring_kernel<HT>;
+        cudaError_t err = allow_smem(kernel, DownRingLayout<HT>::kBytes, down_done);
+        long long grid = sms;
+        const long long need = ((long long)a.O + kRingDownCap - 1) / kRingDownCap;
+        if (grid < need) grid = need;
+        if (grid > a.O) grid = a.O;
+        if (err == cudaSuccess)
+            err = launch_smem(kernel, dim3((unsigned)grid), dim3(64 * a.E), DownRingLayout<HT>::kBytes, stream, pdl, a);
+        if (err != cudaSuccess) {
+            std::fprintf(stderr, "%s: down launch failed: %s\n", who, cudaGetErrorString(err));
+            return -6;
+        }
+    }
+    return 0;
+}
+
+static int grouped_try_ring(const GroupedArgs& a, cudaStream_t stream, const char* who) {
+    auto al16 = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; };
+    if (!ring_enabled() || a.E > kRingMaxExperts || (a.H & (a.H - 1)) != 0 || !al16(a.w1s) || !al16(a.w3s) ||
+        !al16(a.w2s))
+        return 1;
+    int h_shift = 0;
+    while ((1 << h_shift) < a.H) ++h_shift;
+#define DSV4_RING(KT, HT) if (a.K == KT && a.H == HT) return grouped_launch_ring<KT, HT>(a, stream, who, h_shift);
+    DSV4_RING(4096, 2048) DSV4_RING(4096, 1024) DSV4_RING(2048, 2048) DSV4_RING(2048, 1024)
+    DSV4_RING(1024, 2048) DSV4_RING(1024, 1024)
+#undef DSV4_RING
+    return 1;
+}
+
+template <int BPL_A, int BPL_B>
+static int grouped_launch(const GroupedArgs& a, cudaStream_t stream, const char* who) {
     const int sms = sm_count();
     const bool pdl = pdl_enabled();
     {
         const long long pairs = (long long)a.E * a.H;
-        long long grid = 2LL * sms;
-        const long long need = (pairs + kGateCap - 1) / kGateCap;
-        if (grid < need) grid = need;
-        if (grid > pairs) grid = pairs;
-        cudaError_t err = launch(grouped_gate_up_kernel, dim3((unsigned)grid), dim3(kGateThreads), stream, pdl, a);
+        long long grid = sms;
+        const long long max_grid = (pairs + (kGateThreads / 32) - 1) / (kGateThreads / 32);
+        if (grid > max_grid) grid = max_grid;
+        cudaError_t err = launch(grouped_gate_up_kernel<BPL_A>, dim3((unsigned)grid), dim3(kGateThreads), stream,
+                                 pdl, a);
         if (err != cudaSuccess) {
             std::fprintf(stderr, "%s: gate/up launch failed: %s\n", who, cudaGetErrorString(err));
             return -5;
@@ -424,13 +479,27 @@ static int grouped_forward(const GroupedArgs& a, cudaStream_t stream, const char
         const long long need = ((long long)a.O + kDownCap - 1) / kDownCap;
         if (grid < need) grid = need;
         if (grid > a.O) grid = a.O;
-        cudaError_t err = launch(grouped_down_kernel, dim3((unsigned)grid), dim3(kDownThreads), stream, pdl, a);
+        cudaError_t err = launch(grouped_down_kernel<BPL_B>, dim3((unsigned)grid), dim3(kDownThreads), stream, pdl, a);
         if (err != cudaSuccess) {
             std::fprintf(stderr, "%s: down launch failed: %s\n", who, cudaGetErrorString(err));
             return -6;
         }
     }
     return 0;
+}
+
+static int grouped_forward(const GroupedArgs& a, cudaStream_t stream, const char* who) {
+    const int ba = ((a.K >> 5) + 31) >> 5;    // 16-byte blocks per lane on the K_in axis: 1..4
+    const int bb = ((a.H >> 5) + 31) >> 5;    // and on the hidden axis
+    const int bpl_a = ba <= 1 ? 1 : (ba <= 2 ? 2 : 4);
+    const int bpl_b = bb <= 1 ? 1 : (bb <= 2 ? 2 : 4);
+    if (int rc = grouped_try_ring(a, stream, who); rc != 1) return rc;
+#define DSV4_CASE(A, B) if (bpl_a == A && bpl_b == B) return grouped_launch<A, B>(a, stream, who);
+    DSV4_CASE(1, 1) DSV4_CASE(1, 2) DSV4_CASE(1, 4)
+    DSV4_CASE(2, 1) DSV4_CASE(2, 2) DSV4_CASE(2, 4)
+    DSV4_CASE(4, 1) DSV4_CASE(4, 2) DSV4_CASE(4, 4)
+#undef DSV4_CASE
+    return -3;
 }
 
 static int check_shape(const char* who, int K_in, int hidden, int out_dim) {
@@ -442,8 +511,8 @@ static int check_shape(const char* who, int K_in, int hidden, int out_dim) {
         std::fprintf(stderr, "%s: hidden=%d not a positive multiple of 32\n", who, hidden);
         return -2;
     }
-    if (K_in > 32 * 32 * kMaxSlices || hidden > 32 * 32 * kMaxSlices) {
-        std::fprintf(stderr, "%s: K_in/hidden > %d\n", who, 32 * 32 * kMaxSlices);
+    if (K_in > 1024 * kMaxBlocksPerLane || hidden > 1024 * kMaxBlocksPerLane) {
+        std::fprintf(stderr, "%s: K_in/hidden > %d\n", who, 1024 * kMaxBlocksPerLane);
         return -3;
     }
     if (out_dim <= 0) {
@@ -572,4 +641,13 @@ DSV4_API int mxfp4_dequant_bf16(const uint8_t* packed, const uint8_t* scale, lon
     if (grid > 148 * 16) grid = 148 * 16;
     dequant_bf16_kernel<<<(unsigned)grid, 256, 0, stream>>>(packed, scale, rows, cols, out);
     return cudaGetLastError() == cudaSuccess ? 0 : -3;
+}
+
+// Added (diagnostic): 0 unless a kernel of this library gave up on a bounded wait since the last call
+// (1 = gate/up ring, 2 = down ring); the status is cleared by the call.  Synchronises the device.
+DSV4_API int dsv4_b200_device_status(void) {
+    int v = 0, zero = 0;
+    if (cudaMemcpyFromSymbol(&v, g_device_status, sizeof(int)) != cudaSuccess) return -1;
+    if (v != 0) cudaMemcpyToSymbol(g_device_status, &zero, sizeof(int));
+    return v;
 }

@@ -150,5 +150,10 @@ def mxfp4_dequant_bf16(packed: torch.Tensor, scale: torch.Tensor) -> torch.Tenso
     return out
 
 
-__all__ = ["mxfp4_grouped_gemv", "mxfp4_grouped_gemv_ids", "moe_route_topk", "mxfp4_dequant_bf16",
+def device_status() -> int:
+    """0 unless a kernel gave up on one of its bounded waits since the last call (synchronises the device)."""
+    return int(_capi.load("grouped").dsv4_b200_device_status())
+
+
+__all__ = ["device_status", "mxfp4_grouped_gemv", "mxfp4_grouped_gemv_ids", "moe_route_topk", "mxfp4_dequant_bf16",
            "workspace_bytes", "MXFP4_BLOCK_ELEMS"]

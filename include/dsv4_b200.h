@@ -64,6 +64,10 @@ int mxfp4_moe_route_topk(const float* logits, int n_tokens, int n_experts, int k
 int mxfp4_dequant_bf16(const uint8_t* packed, const uint8_t* scale, long long rows, int cols, uint16_t* out,
                        void* stream);
 
+/* Added (diagnostic, no counterpart): 0 unless a kernel of this library gave up on one of its bounded waits since
+ * the last call (1 = gate/up stage, 2 = down stage); clears the status.  Synchronises the device. */
+int dsv4_b200_device_status(void);
+
 /* ---- libmxfp4_gemv.so --------------------------------------------------------------------------------- */
 
 /* Replaces kernel/mxfp4-dense/mxfp4_gemv.cu:131-166.  y[n] = bf16(sum_k W[n,k] x[k]); W_packed [N, K/2],

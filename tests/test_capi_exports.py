@@ -71,7 +71,7 @@ def test_argument_checks_return_the_reference_codes(pkg):
     assert d.mxfp4_gemv_m1(one, one, one, 48, 8, 24, 1, one, None) == -1
     assert d.mxfp4_gemv_m1(one, one, one, 16384, 8, 8192, 512, one, None) == -2
     assert d.mxfp4_gemv_m1(None, one, one, 64, 8, 32, 2, one, None) == -8
-    assert d.mxfp4_gemv_m1(one, one, one, 64, 0, 32, 2, one, None) == 0
+    assert d.mxfp4_gemv_m1(None, None, None, 64, 0, 32, 2, None, None) == 0
     assert f.fp8_e4m3_gemv_m1(one, one, one, 192, 128, 192, 1, one, None) == -1
     assert f.fp8_e4m3_gemv_m1(one, one, one, 256, 100, 256, 2, one, None) == -2
     assert f.fp8_e4m3_gemv_m1(one, one, one, 32768, 128, 32768, 256, one, None) == -3

@@ -27,8 +27,8 @@ def accept(out_bf16, ref_f32, tight=True):
     out = out_bf16.float().cpu().numpy()
     err, cos = oracle.max_abs_rel(out, ref_f32), oracle.cosine(out, ref_f32)
     assert err <= TOL_MAXABS and cos >= TOL_COS, f"max-abs/inf {err:.3e} cosine {cos:.7f}"
-    if tight:   # the kernels are far inside the rule: a bf16 rounding of the output is ~2e-3 of an element
-        assert err <= 4e-3 and cos >= 0.99999, f"(tight) max-abs/inf {err:.3e} cosine {cos:.7f}"
+    if tight:   # the kernels are far inside the rule: one bf16 rounding of an output is up to 2^-8 = 3.9e-3 of it
+        assert err <= 5e-3 and cos >= 0.99999, f"(tight) max-abs/inf {err:.3e} cosine {cos:.7f}"
     return err, cos
 
 
@@ -72,7 +72,8 @@ def test_mxfp4_gemv(rt, qz, dev, K, N):
     p, s = rand_mxfp4(qz, N, K, seed=K + N)
     x = rand_x(K, seed=K)
     y = rt.mxfp4_gemv(p.to(dev), s.to(dev), x.to(dev))
-    accept(y, oracle.mxfp4_gemv_ref(p, s, x))
+    # with a handful of outputs one bf16 rounding (2^-8 of the value) can be the whole max|ref|
+    accept(y, oracle.mxfp4_gemv_ref(p, s, x), tight=N >= 32)
     if ref_kernels.available():
         y_ref = ref_kernels.mxfp4_gemv(x.to(dev), p.to(dev), s.to(dev))
         accept(y, y_ref.float().cpu().numpy(), tight=False)
@@ -84,7 +85,7 @@ def test_mxfp4_gemv_edge_scales_and_values(rt, dev):
     p = rng.integers(0, 256, size=(N, K // 2), dtype=np.uint8)        # every nibble incl. -0.0
     s = rng.integers(118, 130, size=(N, K // 32), dtype=np.uint8)
     s[0, :] = 255                  # NaN sentinel: contributes 0 in kernel semantics
-    s[1, 0], s[1, 1] = 0, 254      # smallest (FP32-subnormal) and largest scale
+    s[1, 0], s[1, 1] = 0, 250      # smallest (FP32-subnormal) scale and a huge one that still fits FP32
     s[2, :] = 0
     x = rand_x(K, 9)
     x[32:64] = 0                   # an all-zero activation block
@@ -193,7 +194,10 @@ def run_grouped(rt, bank_dev, x, r, dev):
                                  {"packed": bank_dev["w2p"], "scale": bank_dev["w2s"]}, None, x.to(dev), r.to(dev))
 
 
-@pytest.mark.parametrize("K,H", [(32, 32), (64, 96), (256, 128), (1024, 992), (4096, 2048)])
+# (1024, 1024), (2048, 1024), (4096, 2048): shapes served by the shared-memory ring kernels; the others by the
+# register-streaming kernels
+@pytest.mark.parametrize("K,H", [(32, 32), (64, 96), (256, 128), (512, 512), (1024, 992), (1024, 1024), (2048, 1024),
+                                 (1024, 1536), (2048, 4096), (4096, 2048)])
 def test_grouped_gemv(rt, qz, dev, K, H):
     bank = qz.make_expert_bank(6, K, H, "cpu", seed=K + H)
     x = rand_x(K, K)
@@ -204,6 +208,7 @@ def test_grouped_gemv(rt, qz, dev, K, H):
     accept(out, ref)
     # deterministic: fixed summation order, no float atomics
     assert torch.equal(out.view(torch.int16), run_grouped(rt, bd, x, r, dev).view(torch.int16))
+    assert rt.device_status() == 0          # no bounded wait ran out
     if ref_kernels.available():
         y_ref = ref_kernels.grouped_gemv(x.to(dev), bd["w1p"], bd["w3p"], bd["w2p"], bd["w1s"], bd["w3s"], bd["w2s"],
                                          r.to(dev))
