@@ -60,11 +60,19 @@ __device__ __forceinline__ float fp16_scale_for(uint32_t amax_bits, float& inv) 
     return __uint_as_float((uint32_t)e << 23);
 }
 
-__device__ __forceinline__ void store8_as_half(__half* dst, const float (&v)[8], float inv) {
+// The fp16 copy of an activation vector in shared memory is stored in 16-byte chunks of 8 values; chunk c of
+// 32-value block b sits at chunk slot (c + (b >> 1)) & 3 of the block, so that the eight lanes of a quarter
+// warp, which read the same chunk of eight consecutive blocks, hit eight different bank groups.
+__device__ __forceinline__ int swizzled_chunk(int idx8) {          // idx8: index of an 8-value chunk
+    const int b = idx8 >> 2, c = idx8 & 3;
+    return (b << 2) | ((c + (b >> 1)) & 3);
+}
+
+__device__ __forceinline__ void store8_as_half(__half* vec, int idx8, const float (&v)[8], float inv) {
     __half2 h[4];
 #pragma unroll
     for (int i = 0; i < 4; ++i) h[i] = __floats2half2_rn(v[2 * i] * inv, v[2 * i + 1] * inv);
-    *reinterpret_cast<uint4*>(dst) = *reinterpret_cast<const uint4*>(h);
+    reinterpret_cast<uint4*>(vec)[swizzled_chunk(idx8)] = *reinterpret_cast<const uint4*>(h);
 }
 
 // Lane's blocks (lane + 32 j) of an fp16 vector in shared memory -> registers.
@@ -72,10 +80,10 @@ template <int BPL>
 __device__ __forceinline__ void lane_blocks_from_smem(const __half* vec, int lane, __half2 (&x)[BPL][16]) {
 #pragma unroll
     for (int j = 0; j < BPL; ++j) {
-        const uint4* src = reinterpret_cast<const uint4*>(vec + (lane + 32 * j) * 32);
+        const uint4* src = reinterpret_cast<const uint4*>(vec);
 #pragma unroll
         for (int c = 0; c < 4; ++c) {
-            const uint4 q = src[c];
+            const uint4 q = src[swizzled_chunk((lane + 32 * j) * 4 + c)];
             x[j][4 * c + 0] = *reinterpret_cast<const __half2*>(&q.x);
             x[j][4 * c + 1] = *reinterpret_cast<const __half2*>(&q.y);
             x[j][4 * c + 2] = *reinterpret_cast<const __half2*>(&q.z);
@@ -151,9 +159,11 @@ __global__ void __launch_bounds__(kRingGateWarps * 32, 1) gate_up_ring_kernel(co
     };
 
     // stacked weights do not depend on the previous kernel in the stream: request them before waiting for it
+#ifndef DSV4_EXP_NOLOAD
     if (a.ids == nullptr) prologue();
     pdl_wait();
     if (a.ids != nullptr) prologue();
+#endif
 
     // x -> fp16 with one scale, once per CTA
     float xs;
@@ -171,7 +181,7 @@ __global__ void __launch_bounds__(kRingGateWarps * 32, 1) gate_up_ring_kernel(co
         for (int w = 0; w < NW; ++w) m = max(m, red[w]);
         float inv;
         xs = fp16_scale_for(m, inv);
-        if (mine) store8_as_half(xh + threadIdx.x * 8, v, inv);
+        if (mine) store8_as_half(xh, threadIdx.x, v, inv);
         __syncthreads();
     }
     __half2 x[BPL][16];
@@ -186,8 +196,11 @@ __global__ void __launch_bounds__(kRingGateWarps * 32, 1) gate_up_ring_kernel(co
         for (int s = 0; s < S; ++s) {
             const int i = i0 + s;
             if (i < n_i && alive) {
+#ifndef DSV4_EXP_NOLOAD
                 alive = mbar_wait_bounded(bars + 8 * s, parity, 1);
+#endif
                 float v[2] = {0.f, 0.f};
+#ifndef DSV4_EXP_NOCOMPUTE
 #pragma unroll
                 for (int j = 0; j < BPL; ++j) {
                     const uint4 wg = lds_v4(lane_w + s * L::kSlot + 512 * j);
@@ -197,6 +210,7 @@ __global__ void __launch_bounds__(kRingGateWarps * 32, 1) gate_up_ring_kernel(co
                     v[0] = fmaf(fp4_block_dot(wg, x[j]), sg, v[0]);
                     v[1] = fmaf(fp4_block_dot(wu, x[j]), su, v[1]);
                 }
+#endif
                 multi_reduce<2>(v, lane);                            // lane 0: gate sum, lane 16: up sum
                 const float up = __shfl_sync(kFullMask, v[0], 16) * xs;
                 if (lane == 0 && alive) {
@@ -204,7 +218,9 @@ __global__ void __launch_bounds__(kRingGateWarps * 32, 1) gate_up_ring_kernel(co
                     a.mid[q0 + i * NW] = (g / (1.0f + __expf(-g))) * up;
                 }
                 __syncwarp();                                        // every lane has read the slot
+#ifndef DSV4_EXP_NOLOAD
                 if (i + S < n_i && alive) issue(q0 + (i + S) * NW, s);
+#endif
             }
         }
     }
@@ -280,22 +296,27 @@ __global__ void __launch_bounds__(2 * kRingMaxExperts * 32, 1) down_ring_kernel(
             if (s < n_i) issue(half + 2 * s, s);
     };
 
+#ifndef DSV4_EXP_NOLOAD
     if (a.ids == nullptr) prologue();
     pdl_wait();
     if (a.ids != nullptr) { eid = a.ids[e]; prologue(); }
+#endif
 
     // SwiGLU intermediate of this warp's expert -> fp16 with one scale per expert; the expert's two warps
     // convert half of it each
-    float ms;
+    float ms = 1.f;
+#ifndef DSV4_EXP_NOSTAGE
     {
-        constexpr int kPer = HT / 64;                                   // elements per lane
-        const float* src = a.mid + (size_t)e * HT + (size_t)(half * 32 + lane) * kPer;
+        // the expert's two warps (64 lanes) read the vector in coalesced 32-byte pieces: piece p of a lane covers
+        // values 8 * (p * 64 + half * 32 + lane) ..., kept in registers between the two steps
+        constexpr int kPieces = HT / 512;
+        const float* src = a.mid + (size_t)e * HT;
+        float v[kPieces][8];
         uint32_t m = 0;
 #pragma unroll
-        for (int c = 0; c < kPer / 8; ++c) {
-            float v[8];
-            load8_as_float(src + 8 * c, v);
-            m = max(m, amax_bits8(v));
+        for (int p = 0; p < kPieces; ++p) {
+            load8_as_float(src + 8 * (p * 64 + half * 32 + lane), v[p]);
+            m = max(m, amax_bits8(v[p]));
         }
 #pragma unroll
         for (int off = 16; off > 0; off >>= 1) m = max(m, __shfl_xor_sync(kFullMask, m, off));
@@ -304,17 +325,17 @@ __global__ void __launch_bounds__(2 * kRingMaxExperts * 32, 1) down_ring_kernel(
         m = max(red[2 * e], red[2 * e + 1]);
         float inv;
         ms = fp16_scale_for(m, inv);
-        __half* dst = mh + (size_t)e * HT + (size_t)(half * 32 + lane) * kPer;
 #pragma unroll
-        for (int c = 0; c < kPer / 8; ++c) {
-            float v[8];
-            load8_as_float(src + 8 * c, v);
-            store8_as_half(dst + 8 * c, v, inv);
-        }
+        for (int p = 0; p < kPieces; ++p) store8_as_half(mh + (size_t)e * HT, p * 64 + half * 32 + lane, v[p], inv);
         __syncthreads();
     }
+#endif
     __half2 m2[BPL][16];
+#ifndef DSV4_EXP_NOSMEMX
     lane_blocks_from_smem<BPL>(mh + (size_t)e * HT, lane, m2);
+#else
+    for (int j = 0; j < BPL; ++j) for (int c = 0; c < 16; ++c) m2[j][c] = __float2half2_rn(1.0f + lane);
+#endif
 
     const uint32_t lane_w = ring + lane * 16;
     const uint32_t lane_s = ring + R * L::kRowP + lane;
@@ -325,18 +346,22 @@ __global__ void __launch_bounds__(2 * kRingMaxExperts * 32, 1) down_ring_kernel(
         for (int s = 0; s < S; ++s) {
             const int i = i0 + s;
             if (i < n_i && alive) {
+#ifndef DSV4_EXP_NOLOAD
                 alive = mbar_wait_bounded(bars + 8 * s, parity, 2);
+#endif
                 const int l0 = (half + 2 * i) * R;
                 float v[R];
 #pragma unroll
                 for (int r = 0; r < R; ++r) {
                     v[r] = 0.f;
+#ifndef DSV4_EXP_NOCOMPUTE
 #pragma unroll
                     for (int j = 0; j < BPL; ++j) {
                         const uint4 w = lds_v4(lane_w + s * L::kSlot + r * L::kRowP + 512 * j);
                         const float sc = e8m0_to_float_fast(lds_u8(lane_s + s * L::kSlot + r * L::kRowS + 32 * j));
                         v[r] = fmaf(fp4_block_dot(w, m2[j]), sc, v[r]);
                     }
+#endif
                 }
                 multi_reduce<R>(v, lane);
                 if (multi_reduce_owner<R>(lane) && alive) {
@@ -344,7 +369,9 @@ __global__ void __launch_bounds__(2 * kRingMaxExperts * 32, 1) down_ring_kernel(
                     if (l < n_local) part[l][e] = v[0] * ms;        // rows past the chunk's end hold stale bytes
                 }
                 __syncwarp();                                        // every lane has read the slot
+#ifndef DSV4_EXP_NOLOAD
                 if (i + S < n_i && alive) issue(half + 2 * (i + S), s);
+#endif
             }
         }
     }
