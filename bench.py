@@ -1,0 +1,405 @@
+#!/usr/bin/env python
+"""Benchmark of the routed-expert MXFP4 MoE decode layer (batch 1) on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
+
+One step = one decode layer for one token: router scores + top-6 on the device, then the routed-expert FFN
+(W1/W3 gate-up, SwiGLU, W2, router-weighted combine) over the 6 selected experts of a resident 256-expert MXFP4
+bank (3.42 GB).  Metric: algorithmic HBM bytes per layer (6 x 13 369 344 + x + out = 80 232 448) / time.
+Prints ONE JSON line (rank 0).  With N > 1 (torchrun) every rank runs its own token on its own bank (replicas:
+single-token decode has no exchange step); the value is the aggregate over ranks, timed as the max over ranks.
+
+`--impl reference` times the reference's CPU path for the same layer (dequantise with the nibble codebook and
+E8M0 scales, FP32 matmul), restated in oracle/, on this machine's host cores.
+"""
+from __future__ import annotations
+
+import argparse
+import importlib
+import json
+import os
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+N_EXPERTS, TOP_K, HIDDEN, EXPERT_FF = 256, 6, 4096, 2048
+BYTES_PER_EXPERT = 2 * (EXPERT_FF * HIDDEN // 2 + EXPERT_FF * HIDDEN // 32) + (HIDDEN * EXPERT_FF // 2 + HIDDEN * EXPERT_FF // 32)
+LAYER_BYTES = TOP_K * BYTES_PER_EXPERT + 2 * HIDDEN * 2                 # weights + x + out = 80 232 448
+GATE_BYTES = TOP_K * 2 * (EXPERT_FF * HIDDEN // 2 + EXPERT_FF * HIDDEN // 32) + HIDDEN * 2 + TOP_K * EXPERT_FF * 4
+# dram__bytes_read.sum + dram__bytes_write.sum of one gate_up_ring_kernel<4096> launch at this shape
+# (profiles/gate_up_ring_kernel_decode_batch1.md)
+GATE_DRAM_TRAFFIC = 53_583_000
+METRIC = "mxfp4_routed_moe_decode_hbm_throughput"
+UNIT = "GB/s"
+SEED = 1236                                                             # 1234 + index of the configuration
+
+
+def measured_hbm_peak():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    try:
+        with open(path) as f:
+            return float(json.load(f)["hbm_gbs"]), "measured (MEASURED_PEAKS.json hbm_gbs)"
+    except Exception:
+        return 6650.0, "fallback (6.65 TB/s, earlier measurement on this pool)"
+
+
+# --------------------------------------------------------------------------------------------- clocks
+
+class ClockSampler:
+    """Polls SM clock and throttle reasons through NVML from a thread while the timed region runs."""
+
+    def __init__(self, index: int):
+        self.samples, self.reasons, self.max_mhz = [], set(), None
+        self._stop = threading.Event()
+        self._thread = None
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            self._nv = pynvml
+            self._h = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self._h, pynvml.NVML_CLOCK_SM)
+        except Exception:
+            self._nv = None
+
+    def _poll(self):
+        nv = self._nv
+        names = {
+            "hw_slowdown": getattr(nv, "nvmlClocksEventReasonHwSlowdown", 0x8),
+            "hw_thermal_slowdown": getattr(nv, "nvmlClocksEventReasonHwThermalSlowdown", 0x40),
+            "sw_thermal_slowdown": getattr(nv, "nvmlClocksEventReasonSwThermalSlowdown", 0x20),
+            "sw_power_cap": getattr(nv, "nvmlClocksEventReasonSwPowerCap", 0x4),
+        }
+        while not self._stop.is_set():
+            try:
+                self.samples.append(nv.nvmlDeviceGetClockInfo(self._h, nv.NVML_CLOCK_SM))
+                try:
+                    mask = nv.nvmlDeviceGetCurrentClocksEventReasons(self._h)
+                except Exception:
+                    mask = nv.nvmlDeviceGetCurrentClocksThrottleReasons(self._h)
+                for name, bit in names.items():
+                    if mask & bit:
+                        self.reasons.add(name)
+            except Exception:
+                pass
+            self._stop.wait(0.02)
+
+    def start(self):
+        if self._nv is not None:
+            self._thread = threading.Thread(target=self._poll, daemon=True)
+            self._thread.start()
+
+    def stop(self):
+        self._stop.set()
+        if self._thread is not None:
+            self._thread.join()
+        s = sorted(self.samples)
+        return {"sm_mhz": s[len(s) // 2] if s else None, "sm_max_mhz": self.max_mhz,
+                "reasons": sorted(self.reasons), "samples": len(s)}
+
+
+# --------------------------------------------------------------------------------------------- CPU path
+
+def cpu_layer_sample(oracle, bank_cpu, x, ids, w, rows_frac: float):
+    """The reference's CPU path on a row-slice of one layer: dequantise (codebook + E8M0), FP32 matmul.
+    rows_frac = 1 is the whole layer; returns the algorithmic bytes it covered."""
+    import numpy as np
+    import torch
+    ff = max(32, int(EXPERT_FF * rows_frac) // 32 * 32)
+    od = max(32, int(HIDDEN * rows_frac) // 32 * 32)
+    xf = x.float().numpy()
+    for j, e in enumerate(ids):
+        g = torch.mv(torch.from_numpy(oracle.dequant_mxfp4(bank_cpu["w1p"][e, :ff], bank_cpu["w1s"][e, :ff], "zero")),
+                     torch.from_numpy(xf)).numpy()
+        u = torch.mv(torch.from_numpy(oracle.dequant_mxfp4(bank_cpu["w3p"][e, :ff], bank_cpu["w3s"][e, :ff], "zero")),
+                     torch.from_numpy(xf)).numpy()
+        m = (g / (1.0 + np.exp(-g))) * u
+        w2 = oracle.dequant_mxfp4(bank_cpu["w2p"][e, :od, : ff // 2], bank_cpu["w2s"][e, :od, : ff // 32], "zero")
+        _ = w[j] * torch.mv(torch.from_numpy(w2), torch.from_numpy(m.astype(np.float32))).numpy()
+    per_row_a = HIDDEN // 2 + HIDDEN // 32
+    return TOP_K * (2 * ff * per_row_a + od * (ff // 2 + ff // 32))
+
+
+def small_cpu_bank(qz, n_experts: int):
+    import torch
+    return qz.make_expert_bank(n_experts, HIDDEN, EXPERT_FF, "cpu", seed=SEED, chunk=2)
+
+
+def run_reference(args, rank: int):
+    """Reference arm: the CPU path, all host threads, bounded samples of the same layer."""
+    if rank != 0:
+        return
+    import torch
+    import numpy as np
+    import __graft_entry__ as entry
+    entry.load_package()
+    qz = importlib.import_module("dsv4_b200.runtime.quantize")
+    import oracle
+
+    bank = small_cpu_bank(qz, TOP_K)
+    g = torch.Generator().manual_seed(SEED)
+    x = torch.randn(HIDDEN, generator=g).to(torch.bfloat16)
+    ids = list(range(TOP_K))
+    w = np.full(TOP_K, 1.0 / TOP_K, dtype=np.float32)
+    # size the per-step sample so that steps + warmup fit in about 90 s
+    t0 = time.perf_counter()
+    cpu_layer_sample(oracle, bank, x, ids, w, 1.0 / 16)
+    t_probe = (time.perf_counter() - t0) * 16                        # estimated seconds per full layer
+    budget = 90.0 / max(1, args.steps + args.warmup)
+    frac = min(1.0, max(1.0 / 64, budget / max(t_probe, 1e-6)))
+    for _ in range(args.warmup):
+        cpu_layer_sample(oracle, bank, x, ids, w, frac)
+    t0 = time.perf_counter()
+    covered = 0
+    for _ in range(args.steps):
+        covered += cpu_layer_sample(oracle, bank, x, ids, w, frac)
+    dt = time.perf_counter() - t0
+    value = covered / dt / 1e9
+    sample = f"{args.steps} steps, each {frac:.4f} of the rows of the 6-expert layer ({covered // max(1, args.steps)} B)"
+    line = {
+        "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": dt / max(1, args.steps) * 1e3, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": workload_config(args.gpus),
+        "cpu_baseline": {"value": value, "unit": UNIT, "cores": torch.get_num_threads(), "kind": "port",
+                         "sample": sample},
+        "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(line), flush=True)
+
+
+def workload_config(n_gpus: int):
+    return {
+        "workload": "routed MoE decode layer, batch 1 (configs[2]): 256 MXFP4 experts W1,W3 [2048x4096] W2 [4096x2048], "
+                    "router logits FP32 [1x256] ~N(0,1), softmax, top-6 renormalised, hidden bf16 [1x4096]",
+        "bytes_per_step": LAYER_BYTES,
+        "l2": "each step picks 6 experts that the previous 8 steps did not use; the bank is 3.42 GB (L2 is 126 MB)",
+        "parallelism": "1 GPU" if n_gpus == 1 else f"{n_gpus} replicas (one token and one bank per GPU, no exchange)",
+        "launch": "CUDA graph of up to 500 steps, replayed",
+    }
+
+
+# --------------------------------------------------------------------------------------------- GPU arm
+
+def make_logits(n_steps: int, device, gen, n_experts: int):
+    """Router logits ~N(0,1) per step; experts used by the previous 8 steps are masked out so that no step
+    finds its weights in L2."""
+    import torch
+    logits = torch.randn(n_steps, n_experts, generator=gen, device=device, dtype=torch.float32)
+    window = max(1, min(8, n_experts // TOP_K - 1))
+    recent = []
+    for i in range(n_steps):
+        if recent:
+            logits[i, torch.cat(recent)] = -30.0
+        top = torch.topk(logits[i], TOP_K).indices
+        recent.append(top)
+        if len(recent) > window:
+            recent.pop(0)
+    return logits
+
+
+def run_gpu(args, rank: int, world: int, local_rank: int):
+    import torch
+    import torch.distributed as dist
+    import __graft_entry__ as entry
+    entry.load_package()
+    rt = importlib.import_module("dsv4_b200.runtime")
+    gb = importlib.import_module("dsv4_b200.runtime.mxfp4_grouped_gemv_binding")
+    qz = importlib.import_module("dsv4_b200.runtime.quantize")
+
+    if not torch.cuda.is_available():
+        raise RuntimeError("bench.py needs a CUDA device (there is no CPU fallback)")
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+
+    gen = torch.Generator(device=dev).manual_seed(SEED + rank)
+    n_experts = args.experts
+    bank = qz.make_expert_bank(n_experts, HIDDEN, EXPERT_FF, dev, seed=SEED + rank, chunk=16)
+    x = torch.randn(HIDDEN, generator=gen, device=dev).to(torch.bfloat16)
+    graph_steps = max(1, min(args.steps, 500))
+    logits = make_logits(graph_steps, dev, gen, n_experts)
+    ids = torch.empty(graph_steps, TOP_K, dtype=torch.int32, device=dev)
+    wts = torch.empty(graph_steps, TOP_K, dtype=torch.float32, device=dev)
+    out = torch.empty(HIDDEN, dtype=torch.bfloat16, device=dev)
+    ws = torch.empty(gb.decode_workspace_bytes(TOP_K, EXPERT_FF, HIDDEN), dtype=torch.uint8, device=dev)
+
+    def layer(i):
+        # router + FFN in one call: the router runs inside the first of the two kernels
+        gb.moe_decode_layer(bank, logits[i], x, k=TOP_K, score_func="softmax", out=out, workspace=ws, check=False)
+
+    # one checked call, then capture; the picks of every step are needed to time the first kernel alone
+    gb.moe_decode_layer(bank, logits[0], x, k=TOP_K, score_func="softmax", out=out, workspace=ws)
+    rt.moe_route_topk(logits, k=TOP_K, score_func="softmax", ids_out=ids, w_out=wts)
+    stream = torch.cuda.Stream(device=dev)
+    with torch.cuda.stream(stream):
+        for i in range(min(3, graph_steps)):
+            layer(i)
+        stream.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=stream):
+            for i in range(graph_steps):
+                layer(i)
+        # a second graph with only the gate/up kernel, to time the dominant kernel alone
+        gate_graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(gate_graph, stream=stream):
+            for i in range(graph_steps):
+                gb.mxfp4_grouped_gemv_ids(bank, ids[i], x, wts[i], out=out, workspace=ws, stage_mask=1, check=False)
+
+        def run_steps(n):
+            full, rest = divmod(n, graph_steps)
+            for _ in range(full):
+                graph.replay()
+            for i in range(rest):
+                layer(i)
+
+        sampler = ClockSampler(local_rank)
+        run_steps(max(args.warmup, 3))
+        stream.synchronize()
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+        sampler.start()
+        t_start, t_end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        t_start.record(stream)
+        run_steps(args.steps)
+        t_end.record(stream)
+        stream.synchronize()
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+        elapsed_ms = t_start.elapsed_time(t_end)
+        # a short timed region gives the sampler nothing: keep the same load running until it has samples
+        t_hold = time.time()
+        while len(sampler.samples) < 5 and time.time() - t_hold < 1.5 and sampler._nv is not None:
+            graph.replay()
+            stream.synchronize()
+        clocks = sampler.stop()
+        clocks["sampled"] = "timed region" if elapsed_ms > 200 else "timed region + the same load held for <= 1.5 s"
+
+        # dominant kernel alone (gate/up + SwiGLU), CUDA events on its stream
+        gate_graph.replay()
+        stream.synchronize()
+        g0, g1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        reps = max(1, min(20, 4000 // graph_steps))
+        g0.record(stream)
+        for _ in range(reps):
+            gate_graph.replay()
+        g1.record(stream)
+        stream.synchronize()
+        gate_us = g0.elapsed_time(g1) * 1e3 / (reps * graph_steps)
+
+        # end to end through the binding with HOST buffers: pinned x and logits in, bf16 out back, every step
+        e2e_steps = max(1, min(args.steps, 200))
+        hx = x.cpu().pin_memory()
+        hl = logits.cpu().pin_memory()
+        hout = torch.empty(HIDDEN, dtype=torch.bfloat16).pin_memory()
+        dx = torch.empty_like(x)
+        dl = torch.empty(1, n_experts, dtype=torch.float32, device=dev)
+
+        def e2e_step(i):
+            dx.copy_(hx, non_blocking=True)
+            dl.copy_(hl[i % graph_steps:i % graph_steps + 1], non_blocking=True)
+            gb.moe_decode_layer(bank, dl[0], dx, k=TOP_K, score_func="softmax", out=out, workspace=ws, check=False)
+            hout.copy_(out, non_blocking=True)
+            stream.synchronize()
+
+        for i in range(5):
+            e2e_step(i)
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(stream)
+        for i in range(e2e_steps):
+            e2e_step(i)
+        e1.record(stream)
+        stream.synchronize()
+        e2e_ms = e0.elapsed_time(e1)
+
+    if gb.device_status() != 0:
+        raise RuntimeError("a kernel gave up on a bounded wait during the benchmark")
+
+    if world > 1:
+        t = torch.tensor([elapsed_ms, e2e_ms, gate_us], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        elapsed_ms, e2e_ms, gate_us = (float(v) for v in t.tolist())
+    if rank != 0:
+        if world > 1:
+            dist.destroy_process_group()
+        return
+
+    peak, peak_src = measured_hbm_peak()
+    value = world * args.steps * LAYER_BYTES / (elapsed_ms * 1e-3) / 1e9
+    e2e_value = world * e2e_steps * LAYER_BYTES / (e2e_ms * 1e-3) / 1e9
+    gate_gbs = GATE_BYTES / (gate_us * 1e-6) / 1e9
+    line = {
+        "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": elapsed_ms / args.steps, "us_per_layer": elapsed_ms / args.steps * 1e3,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f16 products, f32 accumulate",
+        "data": "synthetic", "config": dict(workload_config(world), bank_experts=n_experts),
+        "frac_of_hbm_peak": {"of_measured_copy": value / world / peak, "of_nominal_8TBs": value / world / 8000.0},
+        "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": HIDDEN * 2 + n_experts * 4,
+                "d2h_bytes_per_step": HIDDEN * 2, "steps": e2e_steps,
+                "us_per_layer": e2e_ms / e2e_steps * 1e3,
+                "what": "pinned host x + logits -> device, router, FFN, bf16 out -> pinned host, stream synchronise; every step"},
+        "gpu_launches": 2 * args.steps,
+        "roofline": {"bound": "hbm", "kernel": "gate_up_ring_kernel<4096> (W1/W3 + SwiGLU, 67 % of the layer's bytes)",
+                     "achieved": gate_gbs, "peak": peak, "unit": "GB/s", "frac": gate_gbs / peak,
+                     "traffic": GATE_DRAM_TRAFFIC, "algorithmic_bytes": GATE_BYTES, "us_per_launch": gate_us,
+                     "peak_source": peak_src},
+        "clocks": clocks,
+    }
+    if world == 1:
+        line["cpu_baseline"] = cpu_baseline(qz)
+    print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def cpu_baseline(qz):
+    """The CPU port of the reference path on a bounded sample (two full 6-expert layers), this box's host cores."""
+    import numpy as np
+    import torch
+    import oracle
+    bank = small_cpu_bank(qz, TOP_K)
+    x = torch.randn(HIDDEN, generator=torch.Generator().manual_seed(SEED)).to(torch.bfloat16)
+    ids, w = list(range(TOP_K)), np.full(TOP_K, 1.0 / TOP_K, dtype=np.float32)
+    cpu_layer_sample(oracle, bank, x, ids, w, 1.0 / 16)
+    t0 = time.perf_counter()
+    covered, n = 0, 0
+    while n < 2 or (time.perf_counter() - t0 < 10.0 and n < 8):
+        covered += cpu_layer_sample(oracle, bank, x, ids, w, 1.0)
+        n += 1
+    dt = time.perf_counter() - t0
+    return {"value": covered / dt / 1e9, "unit": UNIT, "cores": torch.get_num_threads(), "kind": "port",
+            "sample": f"{n} full 6-expert layers ({covered} B) in {dt:.1f} s: numpy codebook + E8M0 dequantisation, "
+                      f"torch FP32 matvec", "us_per_layer": dt / n * 1e6}
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20000)
+    ap.add_argument("--warmup", type=int, default=1000)
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--experts", type=int, default=N_EXPERTS,
+                    help="experts in the resident bank; smaller banks (>= 24) are for profiler captures only")
+    args = ap.parse_args()
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if args.impl == "reference":
+        run_reference(args, rank)
+        return
+    if world != args.gpus and world == 1 and args.gpus > 1:
+        raise SystemExit(f"--gpus {args.gpus} needs torchrun with {args.gpus} ranks")
+    run_gpu(args, rank, world, local_rank)
+
+
+if __name__ == "__main__":
+    main()

@@ -11,6 +11,7 @@
 #pragma once
 
 #include "grouped_args.cuh"
+#include "router.cuh"
 #include "stream_ring.cuh"
 
 namespace dsv4 {
@@ -107,16 +108,19 @@ struct GateRingLayout {
 };
 
 template <int KT>
-__global__ void __launch_bounds__(kRingGateWarps * 32, 1) gate_up_ring_kernel(const GroupedArgs a, int h_shift) {
+__global__ void __launch_bounds__(kRingGateWarps * 32, 1) gate_up_ring_kernel(const GroupedArgs a, int h_shift,
+                                                                              const RouteArgs rt) {
     using L = GateRingLayout<KT>;
     constexpr int BPL = L::kBPL;
     constexpr int S = kRingGateStages;
     constexpr int NW = kRingGateWarps;
     extern __shared__ __align__(128) uint8_t ring_smem[];
+    __shared__ int expert_of_slot[8];            // bank index of expert slot e when a table is in use
     pdl_launch_dependents();
 
     const int lane = threadIdx.x & 31;
     const int warp = threadIdx.x >> 5;
+    const bool use_table = a.ids != nullptr || rt.logits != nullptr;
     const uint32_t smem0 = smem_u32(ring_smem);
     const uint32_t ring = smem0 + warp * S * L::kSlot;
     const uint32_t bars = smem0 + L::kBars + warp * S * 8;
@@ -141,7 +145,7 @@ __global__ void __launch_bounds__(kRingGateWarps * 32, 1) gate_up_ring_kernel(co
         if (lane < 4) {
             const int e = q >> h_shift;
             const int h = q - (e << h_shift);
-            const long long eid = a.ids ? (long long)a.ids[e] : (long long)e;
+            const long long eid = use_table ? (long long)expert_of_slot[e] : (long long)e;
             const bool third = (lane & 1) != 0, scale = lane >= 2;
             const uint8_t* base = scale ? (third ? a.w3s : a.w1s) : (third ? a.w3p : a.w1p);
             const uint32_t bytes = scale ? L::kRowS : L::kRowP;
@@ -160,9 +164,27 @@ __global__ void __launch_bounds__(kRingGateWarps * 32, 1) gate_up_ring_kernel(co
 
     // stacked weights do not depend on the previous kernel in the stream: request them before waiting for it
 #ifndef DSV4_EXP_NOLOAD
-    if (a.ids == nullptr) prologue();
+    if (!use_table) prologue();
     pdl_wait();
-    if (a.ids != nullptr) prologue();
+    if (use_table) {
+        if (rt.logits != nullptr) {
+            // fused router: warp 0 of every CTA picks the experts (same result everywhere); CTA 0 publishes
+            // the picks and their weights for the down kernel and the caller
+            if (warp == 0) {
+                int id;
+                float w;
+                route_token<8>(rt.logits, rt.n_experts, rt.k, rt.score_func, rt.eps, rt.scaling, lane, id, w);
+                if (lane < rt.k) {
+                    expert_of_slot[lane] = id;
+                    if (blockIdx.x == 0) { rt.ids_out[lane] = id; rt.w_out[lane] = w; }
+                }
+            }
+        } else if (threadIdx.x < a.E) {
+            expert_of_slot[threadIdx.x] = a.ids[threadIdx.x];
+        }
+        __syncthreads();
+        prologue();
+    }
 #endif
 
     // x -> fp16 with one scale, once per CTA

@@ -19,6 +19,7 @@
 #include "gemv_engine.cuh"
 #include "stream_ring.cuh"
 #include "grouped_args.cuh"
+#include "router.cuh"
 #include "grouped_ring.cuh"
 
 #include <cstdio>
@@ -247,78 +248,20 @@ __global__ void __launch_bounds__(kDownThreads, 1) grouped_down_kernel(const Gro
 // One warp per token.  score_func 0: softmax over all experts, weights renormalised over the top-k.
 // score_func 1: sqrt(softplus(logit)), w = s / (sum s + eps) * scaling (the engine's rule,
 // kernel/cpp-engine-mxfp4/routed.cu:156-208).  Ties go to the lowest expert index in both.
-constexpr int kRouteMaxPerLane = 32;   // up to 1024 experts
-
-__global__ void route_topk_kernel(const float* __restrict__ logits, int n_tokens, int n_experts, int k,
-                                  int score_func, float eps, float scaling,
-                                  int* __restrict__ ids_out, float* __restrict__ w_out) {
+template <int PL>
+__global__ void route_topk_kernel(const RouteArgs r, int n_tokens) {
     pdl_launch_dependents();
     pdl_wait();
     const int lane = threadIdx.x & 31;
     const int token = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
     if (token >= n_tokens) return;
-    const float* row = logits + (size_t)token * n_experts;
-
-    float s[kRouteMaxPerLane];
-    const int per_lane = (n_experts + 31) >> 5;
-    float row_max = -INFINITY;
-#pragma unroll
-    for (int i = 0; i < kRouteMaxPerLane; ++i) {
-        s[i] = -INFINITY;
-        if (i < per_lane) {
-            const int idx = i * 32 + lane;
-            if (idx < n_experts) s[i] = __ldcg(row + idx);
-            row_max = fmaxf(row_max, s[i]);
-        }
-    }
-    if (score_func == 0) {
-        // softmax is monotone in the logit: select on the logits, weight by exp(logit - max); the softmax
-        // denominator cancels when the weights are renormalised over the picks
-        for (int off = 16; off > 0; off >>= 1) row_max = fmaxf(row_max, __shfl_xor_sync(kFullMask, row_max, off));
-    } else {
-#pragma unroll
-        for (int i = 0; i < kRouteMaxPerLane; ++i)
-            if (i < per_lane && s[i] != -INFINITY) {
-                const float g = s[i];
-                s[i] = sqrtf(fmaxf(g, 0.0f) + log1pf(expf(-fabsf(g))));
-            }
-    }
-
-    double picked_sum = 0.0;
-    float my_pick_score = 0.f;   // lane j keeps the j-th pick
-    int my_pick_id = -1;
-    for (int j = 0; j < k; ++j) {
-        float best = -INFINITY;
-        int best_idx = 0x7fffffff;
-#pragma unroll
-        for (int i = 0; i < kRouteMaxPerLane; ++i)
-            if (i < per_lane) {
-                const int idx = i * 32 + lane;
-                if (s[i] > best) { best = s[i]; best_idx = idx; }   // strict: lowest index wins inside a lane
-            }
-        for (int off = 16; off > 0; off >>= 1) {
-            const float ob = __shfl_xor_sync(kFullMask, best, off);
-            const int oi = __shfl_xor_sync(kFullMask, best_idx, off);
-            if (ob > best || (ob == best && oi < best_idx)) { best = ob; best_idx = oi; }
-        }
-        if (lane == (j & 31)) { my_pick_score = best; my_pick_id = best_idx; }
-        if ((best_idx & 31) == lane) {
-#pragma unroll
-            for (int i = 0; i < kRouteMaxPerLane; ++i)
-                if (i == (best_idx >> 5)) s[i] = -INFINITY;
-        }
-        const double contrib = (score_func == 0) ? exp((double)best - (double)row_max) : (double)best;
-        picked_sum += contrib;
-    }
-    if (lane < k) {
-        double w;
-        if (score_func == 0) {
-            w = exp((double)my_pick_score - (double)row_max) / picked_sum;   // softmax renormalised over the picks
-        } else {
-            w = (double)my_pick_score / (picked_sum + (double)eps) * (double)scaling;
-        }
-        ids_out[(size_t)token * k + lane] = my_pick_id;
-        w_out[(size_t)token * k + lane] = (float)w;
+    int id;
+    float w;
+    route_token<PL>(r.logits + (size_t)token * r.n_experts, r.n_experts, r.k, r.score_func, r.eps, r.scaling, lane,
+                    id, w);
+    if (lane < r.k) {
+        r.ids_out[(size_t)token * r.k + lane] = id;
+        r.w_out[(size_t)token * r.k + lane] = w;
     }
 }
 
@@ -410,24 +353,27 @@ static cudaError_t allow_smem(Kernel kernel, size_t bytes, int (&done)[64]) {
 
 // Shared-memory ring path (grouped_ring.cuh).  Returns 1 when the shape is not one it serves.
 template <int KT, int HT>
-static int grouped_launch_ring(const GroupedArgs& a, cudaStream_t stream, const char* who, int h_shift) {
+static int grouped_launch_ring(const GroupedArgs& a, cudaStream_t stream, const char* who, int h_shift,
+                               int stages, const RouteArgs& rt) {
     static int gate_done[64] = {0}, down_done[64] = {0};
     const int sms = sm_count();
     const bool pdl = pdl_enabled();
-    {
+    if (stages & 1) {
         auto kernel = gate_up_ring_kernel<KT>;
         cudaError_t err = allow_smem(kernel, GateRingLayout<KT>::kBytes, gate_done);
         const long long pairs = (long long)a.E * a.H;
         const long long grid = sms < pairs ? sms : pairs;
         if (err == cudaSuccess)
             err = launch_smem(kernel, dim3((unsigned)grid), dim3(kRingGateWarps * 32), GateRingLayout<KT>::kBytes,
-                              stream, pdl, a, h_shift);
+                              stream, pdl, a, h_shift, rt);
         if (err != cudaSuccess) {
             std::fprintf(stderr, "%s: gate/up launch failed: %s\n", who, cudaGetErrorString(err));
             return -5;
         }
     }
-    {
+    if (stages & 2) {
+        GroupedArgs d = a;
+        if (rt.logits != nullptr) { d.ids = rt.ids_out; d.r = rt.w_out; }    // published by the gate kernel
         auto kernel = down_ring_kernel<HT>;
         cudaError_t err = allow_smem(kernel, DownRingLayout<HT>::kBytes, down_done);
         long long grid = sms;
@@ -435,7 +381,7 @@ static int grouped_launch_ring(const GroupedArgs& a, cudaStream_t stream, const 
         if (grid < need) grid = need;
         if (grid > a.O) grid = a.O;
         if (err == cudaSuccess)
-            err = launch_smem(kernel, dim3((unsigned)grid), dim3(64 * a.E), DownRingLayout<HT>::kBytes, stream, pdl, a);
+            err = launch_smem(kernel, dim3((unsigned)grid), dim3(64 * a.E), DownRingLayout<HT>::kBytes, stream, pdl, d);
         if (err != cudaSuccess) {
             std::fprintf(stderr, "%s: down launch failed: %s\n", who, cudaGetErrorString(err));
             return -6;
@@ -444,14 +390,15 @@ static int grouped_launch_ring(const GroupedArgs& a, cudaStream_t stream, const 
     return 0;
 }
 
-static int grouped_try_ring(const GroupedArgs& a, cudaStream_t stream, const char* who) {
+static int grouped_try_ring(const GroupedArgs& a, cudaStream_t stream, const char* who, int stages,
+                            const RouteArgs& rt = RouteArgs{}) {
     auto al16 = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; };
     if (!ring_enabled() || a.E > kRingMaxExperts || (a.H & (a.H - 1)) != 0 || !al16(a.w1s) || !al16(a.w3s) ||
         !al16(a.w2s))
         return 1;
     int h_shift = 0;
     while ((1 << h_shift) < a.H) ++h_shift;
-#define DSV4_RING(KT, HT) if (a.K == KT && a.H == HT) return grouped_launch_ring<KT, HT>(a, stream, who, h_shift);
+#define DSV4_RING(KT, HT) if (a.K == KT && a.H == HT) return grouped_launch_ring<KT, HT>(a, stream, who, h_shift, stages, rt);
     DSV4_RING(4096, 2048) DSV4_RING(4096, 1024) DSV4_RING(2048, 2048) DSV4_RING(2048, 1024)
     DSV4_RING(1024, 2048) DSV4_RING(1024, 1024)
 #undef DSV4_RING
@@ -459,10 +406,10 @@ static int grouped_try_ring(const GroupedArgs& a, cudaStream_t stream, const cha
 }
 
 template <int BPL_A, int BPL_B>
-static int grouped_launch(const GroupedArgs& a, cudaStream_t stream, const char* who) {
+static int grouped_launch(const GroupedArgs& a, cudaStream_t stream, const char* who, int stages) {
     const int sms = sm_count();
     const bool pdl = pdl_enabled();
-    {
+    if (stages & 1) {
         const long long pairs = (long long)a.E * a.H;
         long long grid = sms;
         const long long max_grid = (pairs + (kGateThreads / 32) - 1) / (kGateThreads / 32);
@@ -474,7 +421,7 @@ static int grouped_launch(const GroupedArgs& a, cudaStream_t stream, const char*
             return -5;
         }
     }
-    {
+    if (stages & 2) {
         long long grid = sms;
         const long long need = ((long long)a.O + kDownCap - 1) / kDownCap;
         if (grid < need) grid = need;
@@ -488,13 +435,13 @@ static int grouped_launch(const GroupedArgs& a, cudaStream_t stream, const char*
     return 0;
 }
 
-static int grouped_forward(const GroupedArgs& a, cudaStream_t stream, const char* who) {
+static int grouped_forward(const GroupedArgs& a, cudaStream_t stream, const char* who, int stages = 3) {
     const int ba = ((a.K >> 5) + 31) >> 5;    // 16-byte blocks per lane on the K_in axis: 1..4
     const int bb = ((a.H >> 5) + 31) >> 5;    // and on the hidden axis
     const int bpl_a = ba <= 1 ? 1 : (ba <= 2 ? 2 : 4);
     const int bpl_b = bb <= 1 ? 1 : (bb <= 2 ? 2 : 4);
-    if (int rc = grouped_try_ring(a, stream, who); rc != 1) return rc;
-#define DSV4_CASE(A, B) if (bpl_a == A && bpl_b == B) return grouped_launch<A, B>(a, stream, who);
+    if (int rc = grouped_try_ring(a, stream, who, stages); rc != 1) return rc;
+#define DSV4_CASE(A, B) if (bpl_a == A && bpl_b == B) return grouped_launch<A, B>(a, stream, who, stages);
     DSV4_CASE(1, 1) DSV4_CASE(1, 2) DSV4_CASE(1, 4)
     DSV4_CASE(2, 1) DSV4_CASE(2, 2) DSV4_CASE(2, 4)
     DSV4_CASE(4, 1) DSV4_CASE(4, 2) DSV4_CASE(4, 4)
@@ -570,13 +517,12 @@ DSV4_API size_t mxfp4_grouped_workspace_bytes(int n_exp, int hidden, int out_dim
 // Additive: same computation, but the experts are picked from a resident bank by index, so the caller
 // no longer gathers the selected experts into contiguous scratch first.  `topk_ids` is a DEVICE array of
 // n_exp bank indices (1 <= n_exp <= 8); bank tensors are [n_bank, hidden, K_in/2] etc.
-DSV4_API int mxfp4_grouped_gemv_topk_ids(const __nv_bfloat16* x, const uint8_t* bank_W1_packed,
+static int grouped_ids_impl(const char* who, int stages, const __nv_bfloat16* x, const uint8_t* bank_W1_packed,
                                          const uint8_t* bank_W3_packed, const uint8_t* bank_W2_packed,
                                          const uint8_t* bank_W1_scale, const uint8_t* bank_W3_scale,
                                          const uint8_t* bank_W2_scale, const int* topk_ids, const float* rweights,
                                          int K_in, int hidden, int out_dim, int n_exp, __nv_bfloat16* out,
                                          void* workspace, cudaStream_t stream) {
-    const char* who = "mxfp4_grouped_gemv_topk_ids";
     if (int rc = check_shape(who, K_in, hidden, out_dim)) return rc;
     if (n_exp < 1 || n_exp > kMaxExperts) {
         std::fprintf(stderr, "%s: n_exp=%d outside 1..%d\n", who, n_exp, kMaxExperts);
@@ -597,7 +543,33 @@ DSV4_API int mxfp4_grouped_gemv_topk_ids(const __nv_bfloat16* x, const uint8_t* 
     a.strideBp = (long long)out_dim * (hidden / 2); a.strideBs = (long long)out_dim * (hidden / 32);
     a.mid = reinterpret_cast<float*>(workspace);
     a.out = out;
-    return grouped_forward(a, stream, who);
+    return grouped_forward(a, stream, who, stages);
+}
+
+DSV4_API int mxfp4_grouped_gemv_topk_ids(const __nv_bfloat16* x, const uint8_t* bank_W1_packed,
+                                         const uint8_t* bank_W3_packed, const uint8_t* bank_W2_packed,
+                                         const uint8_t* bank_W1_scale, const uint8_t* bank_W3_scale,
+                                         const uint8_t* bank_W2_scale, const int* topk_ids, const float* rweights,
+                                         int K_in, int hidden, int out_dim, int n_exp, __nv_bfloat16* out,
+                                         void* workspace, cudaStream_t stream) {
+    return grouped_ids_impl("mxfp4_grouped_gemv_topk_ids", 3, x, bank_W1_packed, bank_W3_packed, bank_W2_packed,
+                            bank_W1_scale, bank_W3_scale, bank_W2_scale, topk_ids, rweights, K_in, hidden, out_dim,
+                            n_exp, out, workspace, stream);
+}
+
+// Additive (profiling): the same call restricted to one of its two kernels, so that each can be timed alone.
+// stage_mask 1 = gate/up + SwiGLU only (fills the workspace), 2 = down + combine only (reads it), 3 = both.
+DSV4_API int mxfp4_grouped_gemv_topk_ids_stages(const __nv_bfloat16* x, const uint8_t* bank_W1_packed,
+                                                const uint8_t* bank_W3_packed, const uint8_t* bank_W2_packed,
+                                                const uint8_t* bank_W1_scale, const uint8_t* bank_W3_scale,
+                                                const uint8_t* bank_W2_scale, const int* topk_ids,
+                                                const float* rweights, int K_in, int hidden, int out_dim, int n_exp,
+                                                __nv_bfloat16* out, void* workspace, int stage_mask,
+                                                cudaStream_t stream) {
+    if (stage_mask < 1 || stage_mask > 3) return -9;
+    return grouped_ids_impl("mxfp4_grouped_gemv_topk_ids_stages", stage_mask, x, bank_W1_packed, bank_W3_packed,
+                            bank_W2_packed, bank_W1_scale, bank_W3_scale, bank_W2_scale, topk_ids, rweights, K_in,
+                            hidden, out_dim, n_exp, out, workspace, stream);
 }
 
 // Additive: router scores + top-k + weights on the device (replaces the D2H copy, stream synchronise and
@@ -608,7 +580,7 @@ DSV4_API int mxfp4_grouped_gemv_topk_ids(const __nv_bfloat16* x, const uint8_t* 
 DSV4_API int mxfp4_moe_route_topk(const float* logits, int n_tokens, int n_experts, int k, int score_func,
                                   float eps, float scaling, int* ids_out, float* w_out, cudaStream_t stream) {
     const char* who = "mxfp4_moe_route_topk";
-    if (n_tokens < 0 || n_experts <= 0 || n_experts > 32 * kRouteMaxPerLane || k <= 0 || k > 32 || k > n_experts ||
+    if (n_tokens < 0 || n_experts <= 0 || n_experts > 1024 || k <= 0 || k > 32 || k > n_experts ||
         (score_func != 0 && score_func != 1)) {
         std::fprintf(stderr, "%s: bad shape tokens=%d experts=%d k=%d score_func=%d\n", who, n_tokens, n_experts, k,
                      score_func);
@@ -620,13 +592,72 @@ DSV4_API int mxfp4_moe_route_topk(const float* logits, int n_tokens, int n_exper
         return -2;
     }
     const int warps = 4;
-    cudaError_t err = launch(route_topk_kernel, dim3((n_tokens + warps - 1) / warps), dim3(32 * warps), stream,
-                             pdl_enabled(), logits, n_tokens, n_experts, k, score_func, eps, scaling, ids_out, w_out);
+    RouteArgs r;
+    r.logits = logits; r.n_experts = n_experts; r.k = k; r.score_func = score_func; r.eps = eps; r.scaling = scaling;
+    r.ids_out = ids_out; r.w_out = w_out;
+    const dim3 grid((n_tokens + warps - 1) / warps), block(32 * warps);
+    cudaError_t err = n_experts <= 256 ? launch(route_topk_kernel<8>, grid, block, stream, pdl_enabled(), r, n_tokens)
+                                       : launch(route_topk_kernel<32>, grid, block, stream, pdl_enabled(), r, n_tokens);
     if (err != cudaSuccess) {
         std::fprintf(stderr, "%s: launch failed: %s\n", who, cudaGetErrorString(err));
         return -3;
     }
     return 0;
+}
+
+// Additive: one decode layer for one token in a single call: router (scores, top-k, weights) + routed-expert FFN
+// over a resident bank.  logits FP32 [n_experts]; score_func / eps / scaling as in mxfp4_moe_route_topk; k experts
+// per token (1..6 on the fused path, 1..8 otherwise).  At the shapes served by the shared-memory ring kernels
+// (K_in in {1024, 2048, 4096}, hidden in {1024, 2048}, n_experts <= 256, k <= 6) the router runs inside the first
+// kernel; otherwise a router kernel is launched first.  The picks and their weights are left in the workspace
+// (see mxfp4_moe_decode_workspace_bytes) where the caller may read them after the call: int32 ids at byte offset
+// k * hidden * 4, FP32 weights 32 bytes further.
+DSV4_API size_t mxfp4_moe_decode_workspace_bytes(int k, int hidden, int out_dim) {
+    (void)out_dim;
+    if (k <= 0 || hidden <= 0) return 0;
+    return (size_t)k * (size_t)hidden * sizeof(float) + 64;
+}
+
+DSV4_API int mxfp4_moe_decode_layer(const __nv_bfloat16* x, const uint8_t* bank_W1_packed,
+                                    const uint8_t* bank_W3_packed, const uint8_t* bank_W2_packed,
+                                    const uint8_t* bank_W1_scale, const uint8_t* bank_W3_scale,
+                                    const uint8_t* bank_W2_scale, const float* logits, int n_experts, int score_func,
+                                    float eps, float scaling, int K_in, int hidden, int out_dim, int k,
+                                    __nv_bfloat16* out, void* workspace, cudaStream_t stream) {
+    const char* who = "mxfp4_moe_decode_layer";
+    if (int rc = check_shape(who, K_in, hidden, out_dim)) return rc;
+    if (k < 1 || k > kMaxExperts || k > n_experts || n_experts > 1024 || (score_func != 0 && score_func != 1)) {
+        std::fprintf(stderr, "%s: bad routing shape experts=%d k=%d score_func=%d\n", who, n_experts, k, score_func);
+        return -4;
+    }
+    if (!x || !bank_W1_packed || !bank_W3_packed || !bank_W2_packed || !bank_W1_scale || !bank_W3_scale ||
+        !bank_W2_scale || !logits || !out || !workspace || !aligned16(x) || !aligned16(bank_W1_packed) ||
+        !aligned16(bank_W3_packed) || !aligned16(bank_W2_packed) || !aligned16(workspace)) {
+        std::fprintf(stderr, "%s: null pointer, or x / packed weights / workspace not 16-byte aligned\n", who);
+        return -8;
+    }
+    uint8_t* ws = reinterpret_cast<uint8_t*>(workspace);
+    RouteArgs rt;
+    rt.logits = logits; rt.n_experts = n_experts; rt.k = k; rt.score_func = score_func; rt.eps = eps;
+    rt.scaling = scaling;
+    rt.ids_out = reinterpret_cast<int*>(ws + (size_t)k * hidden * sizeof(float));
+    rt.w_out = reinterpret_cast<float*>(ws + (size_t)k * hidden * sizeof(float) + 32);
+    GroupedArgs a;
+    a.x = x; a.w1p = bank_W1_packed; a.w3p = bank_W3_packed; a.w2p = bank_W2_packed;
+    a.w1s = bank_W1_scale; a.w3s = bank_W3_scale; a.w2s = bank_W2_scale;
+    a.K = K_in; a.H = hidden; a.O = out_dim; a.E = k;
+    a.strideAp = (long long)hidden * (K_in / 2); a.strideAs = (long long)hidden * (K_in / 32);
+    a.strideBp = (long long)out_dim * (hidden / 2); a.strideBs = (long long)out_dim * (hidden / 32);
+    a.mid = reinterpret_cast<float*>(workspace);
+    a.out = out;
+    if (n_experts <= 256) {
+        a.r = nullptr; a.ids = nullptr;                  // both come from the fused router
+        if (int rc = grouped_try_ring(a, stream, who, 3, rt); rc != 1) return rc;
+    }
+    if (int rc = mxfp4_moe_route_topk(logits, 1, n_experts, k, score_func, eps, scaling, rt.ids_out, rt.w_out, stream))
+        return rc;
+    a.r = rt.w_out; a.ids = rt.ids_out;
+    return grouped_forward(a, stream, who);
 }
 
 // Additive (diagnostic): MXFP4 -> bf16 with the reference loader's semantics

@@ -15,6 +15,9 @@ SIGNATURES = {
         "mxfp4_grouped_gemv_topk": (c_int, [_P, _P, _P, _P, _P, _P, _P, _P, c_int, c_int, c_int, c_int, _P, _P, _P]),
         "mxfp4_grouped_workspace_bytes": (c_size_t, [c_int, c_int, c_int]),
         "mxfp4_grouped_gemv_topk_ids": (c_int, [_P, _P, _P, _P, _P, _P, _P, _P, _P, c_int, c_int, c_int, c_int, _P, _P, _P]),
+        "mxfp4_grouped_gemv_topk_ids_stages": (c_int, [_P, _P, _P, _P, _P, _P, _P, _P, _P, c_int, c_int, c_int, c_int, _P, _P, c_int, _P]),
+        "mxfp4_moe_decode_layer": (c_int, [_P] * 8 + [c_int, c_int, c_float, c_float, c_int, c_int, c_int, c_int, _P, _P, _P]),
+        "mxfp4_moe_decode_workspace_bytes": (c_size_t, [c_int, c_int, c_int]),
         "mxfp4_moe_route_topk": (c_int, [_P, c_int, c_int, c_int, c_int, c_float, c_float, _P, _P, _P]),
         "mxfp4_dequant_bf16": (c_int, [_P, _P, c_longlong, c_int, _P, _P]),
         "dsv4_b200_device_status": (c_int, []),

@@ -83,36 +83,42 @@ def mxfp4_grouped_gemv(W1: Dict[str, torch.Tensor], W3: Dict[str, torch.Tensor],
 
 def mxfp4_grouped_gemv_ids(bank: Dict[str, torch.Tensor], ids: torch.Tensor, x: torch.Tensor, r: torch.Tensor,
                            out: Optional[torch.Tensor] = None,
-                           workspace: Optional[torch.Tensor] = None) -> torch.Tensor:
+                           workspace: Optional[torch.Tensor] = None, stage_mask: int = 3,
+                           check: bool = True) -> torch.Tensor:
     """Same FFN, experts `ids` (int32 CUDA [n_exp]) picked from a resident bank
-    {'w1p','w3p','w2p','w1s','w3s','w2s'} stacked over ALL experts."""
+    {'w1p','w3p','w2p','w1s','w3s','w2s'} stacked over ALL experts.  `stage_mask` 1 / 2 runs only the gate-up /
+    the down kernel (profiling); `check=False` skips the Python-side shape checks for callers that made them once."""
     lib = _capi.load("grouped")
-    _check(x, "x", torch.bfloat16)
-    _check(r, "r", torch.float32)
-    _check(ids, "ids", torch.int32)
     K_in = x.numel()
-    _, hidden, out_dim = _check_expert_set({"packed": bank["w1p"], "scale": bank["w1s"]},
-                                           {"packed": bank["w3p"], "scale": bank["w3s"]},
-                                           {"packed": bank["w2p"], "scale": bank["w2s"]}, K_in)
     n_exp = ids.numel()
-    if tuple(r.shape) != (n_exp,):
-        raise ValueError(f"r shape {tuple(r.shape)} != ({n_exp},)")
+    if check:
+        _check(x, "x", torch.bfloat16)
+        _check(r, "r", torch.float32)
+        _check(ids, "ids", torch.int32)
+        _, hidden, out_dim = _check_expert_set({"packed": bank["w1p"], "scale": bank["w1s"]},
+                                               {"packed": bank["w3p"], "scale": bank["w3s"]},
+                                               {"packed": bank["w2p"], "scale": bank["w2s"]}, K_in)
+        if tuple(r.shape) != (n_exp,):
+            raise ValueError(f"r shape {tuple(r.shape)} != ({n_exp},)")
+    else:
+        hidden, out_dim = bank["w1p"].shape[1], bank["w2p"].shape[1]
     if out is None:
         out = torch.empty(out_dim, dtype=torch.bfloat16, device=x.device)
     if workspace is None:
         workspace = torch.empty(workspace_bytes(n_exp, hidden, out_dim), dtype=torch.uint8, device=x.device)
-    rc = lib.mxfp4_grouped_gemv_topk_ids(
+    rc = lib.mxfp4_grouped_gemv_topk_ids_stages(
         _capi.ptr(x), _capi.ptr(bank["w1p"]), _capi.ptr(bank["w3p"]), _capi.ptr(bank["w2p"]),
         _capi.ptr(bank["w1s"]), _capi.ptr(bank["w3s"]), _capi.ptr(bank["w2s"]), _capi.ptr(ids), _capi.ptr(r),
         c_int(K_in), c_int(hidden), c_int(out_dim), c_int(n_exp), _capi.ptr(out), _capi.ptr(workspace),
-        _capi.stream_ptr(x.device))
+        c_int(stage_mask), _capi.stream_ptr(x.device))
     if rc != 0:
         raise RuntimeError(f"mxfp4_grouped_gemv_topk_ids returned {rc}")
     return out
 
 
 def moe_route_topk(logits: torch.Tensor, k: int = 6, score_func: str = "sqrt_softplus", eps: float = 1e-20,
-                   scaling: float = 1.5):
+                   scaling: float = 1.5, ids_out: Optional[torch.Tensor] = None,
+                   w_out: Optional[torch.Tensor] = None):
     """Router on the device: logits float32 [T, E] -> (ids int32 [T, k], weights float32 [T, k]).
 
     score_func 'sqrt_softplus' is the engine's rule (kernel/cpp-engine-mxfp4/routed.cu:156-208, Python twin
@@ -124,13 +130,56 @@ def moe_route_topk(logits: torch.Tensor, k: int = 6, score_func: str = "sqrt_sof
         logits = logits.unsqueeze(0)
     T, E = logits.shape
     func = {"softmax": 0, "sqrt_softplus": 1}[score_func]
-    ids = torch.empty(T, k, dtype=torch.int32, device=logits.device)
-    w = torch.empty(T, k, dtype=torch.float32, device=logits.device)
+    ids = ids_out if ids_out is not None else torch.empty(T, k, dtype=torch.int32, device=logits.device)
+    w = w_out if w_out is not None else torch.empty(T, k, dtype=torch.float32, device=logits.device)
     rc = lib.mxfp4_moe_route_topk(_capi.ptr(logits), c_int(T), c_int(E), c_int(k), c_int(func), c_float(eps),
                                   c_float(scaling), _capi.ptr(ids), _capi.ptr(w), _capi.stream_ptr(logits.device))
     if rc != 0:
         raise RuntimeError(f"mxfp4_moe_route_topk returned {rc}")
     return ids, w
+
+
+def moe_decode_layer(bank: Dict[str, torch.Tensor], logits: torch.Tensor, x: torch.Tensor, k: int = 6,
+                     score_func: str = "sqrt_softplus", eps: float = 1e-20, scaling: float = 1.5,
+                     out: Optional[torch.Tensor] = None, workspace: Optional[torch.Tensor] = None,
+                     check: bool = True) -> torch.Tensor:
+    """One decode layer for one token: router + routed-expert FFN over a resident bank, in one call.
+
+    logits float32 [n_experts], x bfloat16 [K_in]; returns bfloat16 [out_dim].  Pass `workspace` (uint8,
+    `decode_workspace_bytes`) to read the picks afterwards with `decode_picks`."""
+    lib = _capi.load("grouped")
+    K_in, n_experts = x.numel(), logits.numel()
+    hidden, out_dim = bank["w1p"].shape[1], bank["w2p"].shape[1]
+    if check:
+        _check(x, "x", torch.bfloat16)
+        _check(logits, "logits", torch.float32)
+        _check_expert_set({"packed": bank["w1p"], "scale": bank["w1s"]}, {"packed": bank["w3p"], "scale": bank["w3s"]},
+                          {"packed": bank["w2p"], "scale": bank["w2s"]}, K_in)
+        if bank["w1p"].shape[0] != n_experts:
+            raise ValueError(f"bank holds {bank['w1p'].shape[0]} experts, logits {n_experts}")
+    if out is None:
+        out = torch.empty(out_dim, dtype=torch.bfloat16, device=x.device)
+    if workspace is None:
+        workspace = torch.empty(decode_workspace_bytes(k, hidden, out_dim), dtype=torch.uint8, device=x.device)
+    func = {"softmax": 0, "sqrt_softplus": 1}[score_func]
+    rc = lib.mxfp4_moe_decode_layer(
+        _capi.ptr(x), _capi.ptr(bank["w1p"]), _capi.ptr(bank["w3p"]), _capi.ptr(bank["w2p"]), _capi.ptr(bank["w1s"]),
+        _capi.ptr(bank["w3s"]), _capi.ptr(bank["w2s"]), _capi.ptr(logits), c_int(n_experts), c_int(func),
+        c_float(eps), c_float(scaling), c_int(K_in), c_int(hidden), c_int(out_dim), c_int(k), _capi.ptr(out),
+        _capi.ptr(workspace), _capi.stream_ptr(x.device))
+    if rc != 0:
+        raise RuntimeError(f"mxfp4_moe_decode_layer returned {rc}")
+    return out
+
+
+def decode_workspace_bytes(k: int, hidden: int, out_dim: int) -> int:
+    return int(_capi.load("grouped").mxfp4_moe_decode_workspace_bytes(k, hidden, out_dim))
+
+
+def decode_picks(workspace: torch.Tensor, k: int, hidden: int):
+    """(ids int32 [k], weights float32 [k]) left in the workspace by moe_decode_layer."""
+    off = k * hidden * 4
+    return workspace[off:off + 4 * k].view(torch.int32), workspace[off + 32:off + 32 + 4 * k].view(torch.float32)
 
 
 def mxfp4_dequant_bf16(packed: torch.Tensor, scale: torch.Tensor) -> torch.Tensor:
@@ -155,5 +204,5 @@ def device_status() -> int:
     return int(_capi.load("grouped").dsv4_b200_device_status())
 
 
-__all__ = ["device_status", "mxfp4_grouped_gemv", "mxfp4_grouped_gemv_ids", "moe_route_topk", "mxfp4_dequant_bf16",
+__all__ = ["device_status", "moe_decode_layer", "decode_workspace_bytes", "decode_picks", "mxfp4_grouped_gemv", "mxfp4_grouped_gemv_ids", "moe_route_topk", "mxfp4_dequant_bf16",
            "workspace_bytes", "MXFP4_BLOCK_ELEMS"]

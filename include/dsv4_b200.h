@@ -53,12 +53,33 @@ int mxfp4_grouped_gemv_topk_ids(const uint16_t* x, const uint8_t* bank_W1_packed
                                 const float* rweights, int K_in, int hidden, int out_dim, int n_exp, uint16_t* out,
                                 void* workspace, void* stream);
 
+/* Added (profiling, no counterpart): the call above restricted to one of its two kernels so that each can be timed
+ * alone.  stage_mask 1 = gate/up + SwiGLU (fills the workspace), 2 = down + combine (reads it), 3 = both; -9 otherwise. */
+int mxfp4_grouped_gemv_topk_ids_stages(const uint16_t* x, const uint8_t* bank_W1_packed,
+                                       const uint8_t* bank_W3_packed, const uint8_t* bank_W2_packed,
+                                       const uint8_t* bank_W1_scale, const uint8_t* bank_W3_scale,
+                                       const uint8_t* bank_W2_scale, const int* topk_ids, const float* rweights,
+                                       int K_in, int hidden, int out_dim, int n_exp, uint16_t* out, void* workspace,
+                                       int stage_mask, void* stream);
+
 /* Added (replaces the host round trip of kernel/cpp-engine-mxfp4/routed.cu:156-208): router scores, top-k and
  * weights on the device.  logits FP32 [n_tokens, n_experts]; score_func 0 = softmax renormalised over the picks,
  * 1 = sqrt(softplus), w = s / (sum s + eps) * scaling; ids_out int32 [n_tokens, k] by descending score, ties to the
  * lowest index; w_out FP32 [n_tokens, k].  Returns -1 bad shape, -2 null pointer, -3 launch failure. */
 int mxfp4_moe_route_topk(const float* logits, int n_tokens, int n_experts, int k, int score_func, float eps,
                          float scaling, int* ids_out, float* w_out, void* stream);
+
+/* Added (no counterpart; the whole of kernel/cpp-engine-mxfp4/routed.cu:373-503 for one token in one call): router
+ * + routed-expert FFN over a resident bank.  logits FP32 [n_experts]; k experts per token.  At K_in in {1024, 2048,
+ * 4096}, hidden in {1024, 2048}, n_experts <= 256, k <= 6 the router runs inside the first kernel (2 launches),
+ * otherwise a router kernel is launched first (3 launches).  After the call the workspace holds the picks: int32 ids
+ * at byte offset k * hidden * 4, FP32 weights 32 bytes further.  Return codes as mxfp4_grouped_gemv_topk_ids. */
+int mxfp4_moe_decode_layer(const uint16_t* x, const uint8_t* bank_W1_packed, const uint8_t* bank_W3_packed,
+                           const uint8_t* bank_W2_packed, const uint8_t* bank_W1_scale, const uint8_t* bank_W3_scale,
+                           const uint8_t* bank_W2_scale, const float* logits, int n_experts, int score_func, float eps,
+                           float scaling, int K_in, int hidden, int out_dim, int k, uint16_t* out, void* workspace,
+                           void* stream);
+size_t mxfp4_moe_decode_workspace_bytes(int k, int hidden, int out_dim);
 
 /* Added (diagnostic; semantics of runtime/mxfp4_loader.py:272-309, scale 0xFF -> NaN): MXFP4 -> bf16 [rows, cols]. */
 int mxfp4_dequant_bf16(const uint8_t* packed, const uint8_t* scale, long long rows, int cols, uint16_t* out,

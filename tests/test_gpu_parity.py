@@ -287,3 +287,29 @@ def test_router_other_shapes(rt, dev):
         ref_ids, ref_w = oracle.route_softmax(logits, k)
         assert np.array_equal(ids.cpu().numpy(), ref_ids)
         np.testing.assert_allclose(w.cpu().numpy(), ref_w, rtol=2e-6)
+
+
+# ------------------------------------------------------------------------------------------------ one-call layer
+
+@pytest.mark.parametrize("K,H,E,func", [(1024, 1024, 32, "softmax"), (4096, 2048, 16, "sqrt_softplus"),
+                                        (256, 128, 12, "softmax"), (1024, 1024, 300, "sqrt_softplus")])
+def test_decode_layer_one_call(rt, qz, dev, K, H, E, func):
+    """Router + FFN in one call (fused router at ring shapes, separate router kernel otherwise) against the oracle
+    and, bit for bit, against the two-call sequence."""
+    bank = qz.make_expert_bank(E, K, H, "cpu", seed=E)
+    bd = {k: v.to(dev) for k, v in bank.items()}
+    x = rand_x(K, 3)
+    logits = torch.randn(E, generator=torch.Generator().manual_seed(5))
+    ws = torch.empty(rt.decode_workspace_bytes(6, H, K), dtype=torch.uint8, device=dev)
+    out = rt.moe_decode_layer(bd, logits.to(dev), x.to(dev), k=6, score_func=func, workspace=ws)
+    ids, w = rt.decode_picks(ws, 6, H)
+    ref_ids, ref_w = (oracle.route_softmax if func == "softmax" else oracle.route_sqrt_softplus)(logits.numpy()[None])
+    assert np.array_equal(ids.cpu().numpy(), ref_ids[0])                       # identical expert selection
+    np.testing.assert_allclose(w.cpu().numpy(), ref_w[0], rtol=2e-6)
+    st = stacked(bank, ref_ids[0].tolist())
+    ref = oracle.grouped_gemv_ref(x, st["w1p"], st["w3p"], st["w2p"], st["w1s"], st["w3s"], st["w2s"], ref_w[0])
+    accept(out, ref)
+    ids2, w2 = rt.moe_route_topk(logits.to(dev), k=6, score_func=func)
+    out2 = rt.mxfp4_grouped_gemv_ids(bd, ids2[0].contiguous(), x.to(dev), w2[0].contiguous())
+    assert torch.equal(out.view(torch.int16), out2.view(torch.int16))
+    assert rt.device_status() == 0
