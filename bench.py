@@ -31,7 +31,7 @@ BYTES_PER_EXPERT = 2 * (EXPERT_FF * HIDDEN // 2 + EXPERT_FF * HIDDEN // 32) + (H
 LAYER_BYTES = TOP_K * BYTES_PER_EXPERT + 2 * HIDDEN * 2                 # weights + x + out = 80 232 448
 GATE_BYTES = TOP_K * 2 * (EXPERT_FF * HIDDEN // 2 + EXPERT_FF * HIDDEN // 32) + HIDDEN * 2 + TOP_K * EXPERT_FF * 4
 # dram__bytes_read.sum + dram__bytes_write.sum of one gate_up_ring_kernel<4096> launch at this shape
-# (profiles/gate_up_ring_kernel_decode_batch1.md)
+# (taken from an ncu capture of that launch on a 24-expert bank)
 GATE_DRAM_TRAFFIC = 53_583_000
 METRIC = "mxfp4_routed_moe_decode_hbm_throughput"
 UNIT = "GB/s"
