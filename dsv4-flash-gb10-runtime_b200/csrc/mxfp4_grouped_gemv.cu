@@ -682,3 +682,81 @@ DSV4_API int dsv4_b200_device_status(void) {
     if (v != 0) cudaMemcpyToSymbol(g_device_status, &zero, sizeof(int));
     return v;
 }
+
+// ------------------------------------------------------------------------------------------------
+// Entry point that needs no workspace from the caller
+// ------------------------------------------------------------------------------------------------
+// Some hosts cannot hand this library a scratch buffer at call time: an engine that gave all free HBM to its
+// expert bank and KV cache at start-up has nothing left to carve a workspace from, and a decode thread must not
+// enter cudaMalloc because that call synchronises the whole device.  For them the SwiGLU intermediate lives in
+// this fixed array inside the library image.  Every GPU that loads the library carries these 96 KB until the
+// process exits.
+constexpr int kStaticMaxExperts = 6;
+constexpr int kStaticMaxHidden = 4096;
+static __device__ __align__(256) unsigned char g_static_scratch[kStaticMaxExperts * kStaticMaxHidden * sizeof(float)];
+
+// Device address of g_static_scratch on the current device, or nullptr (with a message) if the runtime refuses.
+// In host code the array's name is only a handle for the runtime, not an address a kernel could use, so the
+// address is asked for once per device, with that device current, and remembered.
+static void* static_scratch_address() {
+    static void* cached[64] = {nullptr};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) {
+        std::fprintf(stderr, "mxfp4_grouped_gemv_topk_static: cannot identify the current device\n");
+        return nullptr;
+    }
+    void* p = __atomic_load_n(&cached[dev], __ATOMIC_ACQUIRE);
+    if (p != nullptr) return p;
+    const cudaError_t err = cudaGetSymbolAddress(&p, g_static_scratch);
+    if (err != cudaSuccess || p == nullptr) {
+        std::fprintf(stderr, "mxfp4_grouped_gemv_topk_static: cudaGetSymbolAddress failed: %s\n",
+                     cudaGetErrorString(err));
+        return nullptr;
+    }
+    __atomic_store_n(&cached[dev], p, __ATOMIC_RELEASE);
+    return p;
+}
+
+// The routed-expert FFN of mxfp4_grouped_gemv_topk without the workspace argument: same inputs, same output,
+// same kernels, bit-identical result.  It allocates nothing and frees nothing.
+//   * Limits: n_exp == 6 (as the workspace entry), hidden <= 4096; a larger hidden returns -10 with a message.
+//   * The first call on each device looks up the array's device address (one cudaGetSymbolAddress); make that
+//     first call before any stream capture begins on that device.
+//   * All calls on a device share the one array.  Nothing in it has to be zero beforehand (the first kernel
+//     overwrites every element the second one reads), but two calls whose kernels overlap on the GPU - different
+//     streams, or the same stream from two threads without ordering - race on it and corrupt each other's
+//     intermediate.  Serialise such calls, or use mxfp4_grouped_gemv_topk with one workspace per stream.
+//   * Other return codes as mxfp4_grouped_gemv_topk; -11 if the array's address cannot be obtained.
+DSV4_API int mxfp4_grouped_gemv_topk_static(const __nv_bfloat16* x, const uint8_t* W1_packed,
+                                            const uint8_t* W3_packed, const uint8_t* W2_packed,
+                                            const uint8_t* W1_scale, const uint8_t* W3_scale,
+                                            const uint8_t* W2_scale, const float* rweights, int K_in, int hidden,
+                                            int out_dim, int n_exp, __nv_bfloat16* out, cudaStream_t stream) {
+    const char* who = "mxfp4_grouped_gemv_topk_static";
+    if (hidden > kStaticMaxHidden || n_exp > kStaticMaxExperts) {
+        std::fprintf(stderr, "%s: n_exp=%d hidden=%d exceed the built-in scratch (%d experts x %d)\n", who, n_exp,
+                     hidden, kStaticMaxExperts, kStaticMaxHidden);
+        return -10;
+    }
+    if (int rc = check_shape(who, K_in, hidden, out_dim)) return rc;
+    if (n_exp != 6) {
+        std::fprintf(stderr, "%s: n_exp=%d != 6\n", who, n_exp);
+        return -4;
+    }
+    if (!x || !W1_packed || !W3_packed || !W2_packed || !W1_scale || !W3_scale || !W2_scale || !rweights || !out ||
+        !aligned16(x) || !aligned16(W1_packed) || !aligned16(W3_packed) || !aligned16(W2_packed)) {
+        std::fprintf(stderr, "%s: null pointer, or x / packed weights not 16-byte aligned\n", who);
+        return -8;
+    }
+    void* scratch = static_scratch_address();
+    if (scratch == nullptr) return -11;
+    GroupedArgs a;
+    a.x = x; a.w1p = W1_packed; a.w3p = W3_packed; a.w2p = W2_packed;
+    a.w1s = W1_scale; a.w3s = W3_scale; a.w2s = W2_scale; a.r = rweights; a.ids = nullptr;
+    a.K = K_in; a.H = hidden; a.O = out_dim; a.E = n_exp;
+    a.strideAp = (long long)hidden * (K_in / 2); a.strideAs = (long long)hidden * (K_in / 32);
+    a.strideBp = (long long)out_dim * (hidden / 2); a.strideBs = (long long)out_dim * (hidden / 32);
+    a.mid = reinterpret_cast<float*>(scratch);
+    a.out = out;
+    return grouped_forward(a, stream, who);
+}

@@ -13,6 +13,7 @@ _P = c_void_p
 SIGNATURES = {
     "grouped": {
         "mxfp4_grouped_gemv_topk": (c_int, [_P, _P, _P, _P, _P, _P, _P, _P, c_int, c_int, c_int, c_int, _P, _P, _P]),
+        "mxfp4_grouped_gemv_topk_static": (c_int, [_P, _P, _P, _P, _P, _P, _P, _P, c_int, c_int, c_int, c_int, _P, _P]),
         "mxfp4_grouped_workspace_bytes": (c_size_t, [c_int, c_int, c_int]),
         "mxfp4_grouped_gemv_topk_ids": (c_int, [_P, _P, _P, _P, _P, _P, _P, _P, _P, c_int, c_int, c_int, c_int, _P, _P, _P]),
         "mxfp4_grouped_gemv_topk_ids_stages": (c_int, [_P, _P, _P, _P, _P, _P, _P, _P, _P, c_int, c_int, c_int, c_int, _P, _P, c_int, _P]),

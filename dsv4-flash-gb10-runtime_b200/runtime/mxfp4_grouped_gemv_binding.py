@@ -81,6 +81,34 @@ def mxfp4_grouped_gemv(W1: Dict[str, torch.Tensor], W3: Dict[str, torch.Tensor],
     return out
 
 
+def mxfp4_grouped_gemv_static(W1: Dict[str, torch.Tensor], W3: Dict[str, torch.Tensor], W2: Dict[str, torch.Tensor],
+                              x: torch.Tensor, r: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+    """The routed-expert FFN through the entry point that takes no workspace and allocates nothing.
+
+    For hosts that cannot get device memory at call time (everything already committed to the expert bank and the
+    KV cache, or a thread that must not enter cudaMalloc): the intermediate sits in a fixed 96 KB array inside the
+    library, shared by every call on the device, so calls that overlap on the GPU must be serialised by the caller.
+    `out` (bfloat16 [out_dim]) is mandatory so that this wrapper allocates nothing either.  hidden <= 4096,
+    six experts.  Make the first call on a device before capturing a stream there."""
+    lib = _capi.load("grouped")
+    _check(x, "x", torch.bfloat16)
+    _check(r, "r", torch.float32)
+    K_in = x.numel()
+    n_exp, hidden, out_dim = _check_expert_set(W1, W3, W2, K_in)
+    if tuple(r.shape) != (n_exp,):
+        raise ValueError(f"r shape {tuple(r.shape)} != ({n_exp},)")
+    _check(out, "out", torch.bfloat16)
+    if tuple(out.shape) != (out_dim,):
+        raise ValueError(f"out shape {tuple(out.shape)} != ({out_dim},)")
+    rc = lib.mxfp4_grouped_gemv_topk_static(
+        _capi.ptr(x), _capi.ptr(W1["packed"]), _capi.ptr(W3["packed"]), _capi.ptr(W2["packed"]),
+        _capi.ptr(W1["scale"]), _capi.ptr(W3["scale"]), _capi.ptr(W2["scale"]), _capi.ptr(r),
+        c_int(K_in), c_int(hidden), c_int(out_dim), c_int(n_exp), _capi.ptr(out), _capi.stream_ptr(x.device))
+    if rc != 0:
+        raise RuntimeError(f"mxfp4_grouped_gemv_topk_static returned {rc}")
+    return out
+
+
 def mxfp4_grouped_gemv_ids(bank: Dict[str, torch.Tensor], ids: torch.Tensor, x: torch.Tensor, r: torch.Tensor,
                            out: Optional[torch.Tensor] = None,
                            workspace: Optional[torch.Tensor] = None, stage_mask: int = 3,
@@ -204,5 +232,5 @@ def device_status() -> int:
     return int(_capi.load("grouped").dsv4_b200_device_status())
 
 
-__all__ = ["device_status", "moe_decode_layer", "decode_workspace_bytes", "decode_picks", "mxfp4_grouped_gemv", "mxfp4_grouped_gemv_ids", "moe_route_topk", "mxfp4_dequant_bf16",
+__all__ = ["device_status", "moe_decode_layer", "decode_workspace_bytes", "decode_picks", "mxfp4_grouped_gemv", "mxfp4_grouped_gemv_static", "mxfp4_grouped_gemv_ids", "moe_route_topk", "mxfp4_dequant_bf16",
            "workspace_bytes", "MXFP4_BLOCK_ELEMS"]

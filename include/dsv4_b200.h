@@ -42,6 +42,19 @@ int mxfp4_grouped_gemv_topk(const uint16_t* x, const uint8_t* W1_packed, const u
                             const uint8_t* W2_scale, const float* rweights, int K_in, int hidden, int out_dim,
                             int n_exp, uint16_t* out, void* workspace, void* stream);
 
+/* Has no counterpart in the reference.  mxfp4_grouped_gemv_topk for hosts that cannot supply a workspace at call
+ * time (all free HBM already given to the expert bank and KV cache, or a decode thread that must stay out of
+ * cudaMalloc because it synchronises the device): the FP32 intermediate lives in a 96 KB array inside the library
+ * image, present on every GPU that loads the library.  Allocates and frees nothing.  Limits: n_exp == 6,
+ * hidden <= 4096 (-10 beyond that).  The first call on a device fetches the array's address: make it before any
+ * stream capture on that device.  All calls on a device share the array, so calls whose kernels overlap on the GPU
+ * race; serialise them or use the workspace entry.  -11 if the array's address cannot be obtained; other codes as
+ * mxfp4_grouped_gemv_topk, whose result it reproduces bit for bit. */
+int mxfp4_grouped_gemv_topk_static(const uint16_t* x, const uint8_t* W1_packed, const uint8_t* W3_packed,
+                                   const uint8_t* W2_packed, const uint8_t* W1_scale, const uint8_t* W3_scale,
+                                   const uint8_t* W2_scale, const float* rweights, int K_in, int hidden, int out_dim,
+                                   int n_exp, uint16_t* out, void* stream);
+
 /* Replaces kernel/mxfp4-routed/mxfp4_grouped_gemv.cu:406-409.  Bytes the caller must provide as `workspace`. */
 size_t mxfp4_grouped_workspace_bytes(int n_exp, int hidden, int out_dim);
 
