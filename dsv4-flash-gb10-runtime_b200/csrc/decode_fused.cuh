@@ -1,0 +1,311 @@
+// One persistent kernel for the whole routed-expert decode layer of one token:
+//   router (optional)  ->  gate/up + SwiGLU  ->  grid barrier  ->  down + router-weighted combine.
+// It replaces the two chained kernels of grouped_ring.cuh at the same shapes; what it saves is the second launch,
+// the drain between the kernels and the second set-up: while a CTA waits at the grid barrier for the other CTAs'
+// SwiGLU rows, its copies of the first W2 rows are already in flight.
+//
+// Launched cooperatively with one CTA per SM (the runtime guarantees that all CTAs are resident, which is what
+// makes the grid barrier legal); the barrier itself is cooperative_groups::grid_group::sync().
+//
+// 16 warps per CTA.  Each warp owns a private 8.5 KB ring: two slots of one (W1 row, W3 row, 2 scale rows) pair in
+// the first phase, four slots of two (W2 row, scale row) in the second.  Second-phase work is cut into
+// (expert, 2-row chunk) tasks dealt round-robin to the warps; a warp reloads the expert's fp16 intermediate from
+// shared memory into registers at the start of every task (8 x 128-bit loads against ~200 arithmetic instructions).
+#pragma once
+
+#include <cooperative_groups.h>
+
+#include "grouped_ring.cuh"
+
+namespace dsv4 {
+
+constexpr int kFusedWarps = 16;
+constexpr int kFusedStagesA = 2;
+constexpr int kFusedRowsB = 2;
+constexpr int kFusedCap = 64;          // output rows per CTA
+
+template <int KT, int HT>
+struct FusedLayout {
+    static constexpr int kBplA = KT / 1024, kBplB = HT / 1024;
+    static constexpr uint32_t kRowPA = KT / 2, kRowSA = KT / 32, kSlotA = 2 * (kRowPA + kRowSA);
+    static constexpr uint32_t kRowPB = HT / 2, kRowSB = HT / 32, kSlotB = kFusedRowsB * (kRowPB + kRowSB);
+    static constexpr uint32_t kRingPerWarp = (kFusedStagesA * kSlotA > 2 * kSlotB) ? kFusedStagesA * kSlotA : 2 * kSlotB;
+    static constexpr int kStagesA = (kRingPerWarp / kSlotA > 4) ? 4 : kRingPerWarp / kSlotA;
+    static constexpr int kStagesB = (kRingPerWarp / kSlotB > 6) ? 6 : kRingPerWarp / kSlotB;
+    static constexpr uint32_t kRing = kFusedWarps * kRingPerWarp;
+    static constexpr uint32_t kVecBytes = (KT * 2 > kRingMaxExperts * HT * 2) ? KT * 2 : kRingMaxExperts * HT * 2;
+    static constexpr uint32_t kVec = kRing;                              // fp16 x, later the fp16 intermediates
+    static constexpr uint32_t kBars = kVec + kVecBytes;                  // per warp: kStagesA + kStagesB barriers
+    static constexpr uint32_t kBarsPerWarp = kStagesA + kStagesB;
+    static constexpr uint32_t kRed = kBars + kFusedWarps * kBarsPerWarp * 8;
+    static constexpr uint32_t kPart = kRed + 64 * 4;                     // [rows][8] FP32
+    static constexpr uint32_t kBytes = kPart + kFusedCap * 8 * 4;
+    static_assert(kStagesA >= 2 && kStagesB >= 2, "ring too small");
+};
+
+template <int KT, int HT>
+__global__ void __launch_bounds__(kFusedWarps * 32, 1) moe_decode_fused_kernel(const GroupedArgs a, int h_shift,
+                                                                               const RouteArgs rt) {
+    using L = FusedLayout<KT, HT>;
+    constexpr int NW = kFusedWarps;
+    constexpr int SA = L::kStagesA, SB = L::kStagesB, R = kFusedRowsB;
+    extern __shared__ __align__(128) uint8_t ring_smem[];
+    __shared__ int expert_of_slot[8];
+    __shared__ float weight_of_slot[8];
+    __shared__ float mid_scale[8];
+    __shared__ int next_pair, next_task;          // work queues of the two phases
+    pdl_launch_dependents();
+
+    const int lane = threadIdx.x & 31;
+    const int warp = threadIdx.x >> 5;
+    const bool routed = rt.logits != nullptr;
+    const bool use_table = a.ids != nullptr || routed;
+    const uint32_t smem0 = smem_u32(ring_smem);
+    const uint32_t ring = smem0 + warp * L::kRingPerWarp;
+    const uint32_t bars_a = smem0 + L::kBars + warp * L::kBarsPerWarp * 8;
+    const uint32_t bars_b = bars_a + SA * 8;
+    __half* vec = reinterpret_cast<__half*>(ring_smem + L::kVec);
+    uint32_t* red = reinterpret_cast<uint32_t*>(ring_smem + L::kRed);
+    float (*part)[8] = reinterpret_cast<float (*)[8]>(ring_smem + L::kPart);
+
+    if (lane == 0) {
+#pragma unroll
+        for (int s = 0; s < SA + SB; ++s) mbar_init(bars_a + 8 * s, 1);
+    }
+    mbar_init_fence();
+    __syncwarp();
+
+    // ------------------------------------------------------------------ phase A: gate / up + SwiGLU
+    const long long total = (long long)a.E << h_shift;
+    const int q_begin = (int)(total * blockIdx.x / gridDim.x);
+    const int q_end = (int)(total * (blockIdx.x + 1) / gridDim.x);
+    if (threadIdx.x == 0) { next_pair = q_begin; next_task = 0; }
+    // work is handed out from a shared counter at the moment a ring slot is (re)filled, so that the warps of a
+    // CTA finish together
+    auto claim = [&](int* counter) -> int {
+        int v = 0;
+        if (lane == 0) v = atomicAdd(counter, 1);
+        return __shfl_sync(kFullMask, v, 0);
+    };
+
+    auto issue_a = [&](int q, int s) {
+        if (lane < 4) {
+            const int e = q >> h_shift;
+            const int h = q - (e << h_shift);
+            const long long eid = use_table ? (long long)expert_of_slot[e] : (long long)e;
+            const bool third = (lane & 1) != 0, scale = lane >= 2;
+            const uint8_t* base = scale ? (third ? a.w3s : a.w1s) : (third ? a.w3p : a.w1p);
+            const uint32_t bytes = scale ? L::kRowSA : L::kRowPA;
+            const uint8_t* src = base + eid * (scale ? a.strideAs : a.strideAp) + (long long)h * bytes;
+            const uint32_t dst = ring + s * L::kSlotA + (scale ? 2 * L::kRowPA : 0) + (third ? bytes : 0);
+            const uint32_t bar = bars_a + 8 * s;
+            if (lane == 0) mbar_arrive_expect_tx(bar, L::kSlotA);
+            bulk_copy_g2s(dst, src, bytes, bar);
+        }
+    };
+    int qa[SA];
+    auto prologue_a = [&]() {
+#pragma unroll
+        for (int s = 0; s < SA; ++s) {
+            qa[s] = claim(&next_pair);
+            if (qa[s] < q_end) issue_a(qa[s], s);
+        }
+    };
+
+    pdl_wait();
+    if (routed) {
+        if (warp == 0) {
+            int id;
+            float w;
+            route_token<8>(rt.logits, rt.n_experts, rt.k, rt.score_func, rt.eps, rt.scaling, lane, id, w);
+            if (lane < rt.k) {
+                expert_of_slot[lane] = id;
+                weight_of_slot[lane] = w;
+                if (blockIdx.x == 0) { rt.ids_out[lane] = id; rt.w_out[lane] = w; }
+            }
+        }
+    } else if (threadIdx.x < a.E) {
+        expert_of_slot[threadIdx.x] = a.ids ? a.ids[threadIdx.x] : (int)threadIdx.x;
+        weight_of_slot[threadIdx.x] = __ldcg(a.r + threadIdx.x);
+    }
+
+    // x -> fp16 with one scale, once per CTA (the barrier also publishes the expert table)
+    // (x is requested before the weight copies are queued: a load issued behind 20 MB of queued copies waits for them)
+    float xs;
+    {
+        float v[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+        const bool mine = threadIdx.x * 8 < KT;
+        if (mine) load8_as_float(a.x + threadIdx.x * 8, v);
+        uint32_t m = amax_bits8(v);
+#pragma unroll
+        for (int off = 16; off > 0; off >>= 1) m = max(m, __shfl_xor_sync(kFullMask, m, off));
+        if (lane == 0) red[warp] = m;
+        __syncthreads();
+        prologue_a();
+        m = 0;
+#pragma unroll
+        for (int w = 0; w < NW; ++w) m = max(m, red[w]);
+        float inv;
+        xs = fp16_scale_for(m, inv);
+        if (mine) store8_as_half(vec, threadIdx.x, v, inv);
+        __syncthreads();
+    }
+    bool alive = true;
+    {
+        __half2 x[L::kBplA][16];
+        lane_blocks_from_smem<L::kBplA>(vec, lane, x);
+        const uint32_t lane_w = ring + lane * 16;
+        const uint32_t lane_s = ring + 2 * L::kRowPA + lane;
+        uint32_t parity = 0;
+        for (bool any = true; any; parity ^= 1) {
+            any = false;
+#pragma unroll
+            for (int s = 0; s < SA; ++s) {
+                const int q = qa[s];
+                if (q < q_end && alive) {
+                    any = true;
+                    alive = mbar_wait_bounded(bars_a + 8 * s, parity, 1);
+                    float v[2] = {0.f, 0.f};
+#pragma unroll
+                    for (int j = 0; j < L::kBplA; ++j) {
+                        const uint4 wg = lds_v4(lane_w + s * L::kSlotA + 512 * j);
+                        const uint4 wu = lds_v4(lane_w + s * L::kSlotA + L::kRowPA + 512 * j);
+                        const float sg = e8m0_to_float_fast(lds_u8(lane_s + s * L::kSlotA + 32 * j));
+                        const float su = e8m0_to_float_fast(lds_u8(lane_s + s * L::kSlotA + L::kRowSA + 32 * j));
+                        v[0] = fmaf(fp4_block_dot(wg, x[j]), sg, v[0]);
+                        v[1] = fmaf(fp4_block_dot(wu, x[j]), su, v[1]);
+                    }
+                    multi_reduce<2>(v, lane);                        // lane 0: gate sum, lane 16: up sum
+                    const float up = __shfl_sync(kFullMask, v[0], 16) * xs;
+                    if (lane == 0 && alive) {
+                        const float g = v[0] * xs;
+                        a.mid[q] = (g / (1.0f + __expf(-g))) * up;
+                    }
+                    __syncwarp();                                    // every lane has read the slot
+                    qa[s] = claim(&next_pair);
+                    if (qa[s] < q_end && alive) issue_a(qa[s], s);
+                }
+            }
+        }
+    }
+    // ------------------------------------------------------------------ phase B set-up: request W2 rows, then wait
+    const int o_begin = (int)((long long)a.O * blockIdx.x / gridDim.x);
+    const int o_end = (int)((long long)a.O * (blockIdx.x + 1) / gridDim.x);
+    const int n_local = o_end - o_begin;
+    const int n_chunks = (n_local + R - 1) / R;
+    const int n_tasks = a.E * n_chunks;                              // task t: expert t % E, chunk t / E
+    const uint32_t inv_e = (65536u + a.E - 1) / a.E;                 // t / E == (t * inv_e) >> 16 for t < 4096, E <= 8
+
+    auto issue_b = [&](int t, int s) {
+        if (lane < 2) {
+            const int c = (int)(((uint32_t)t * inv_e) >> 16);
+            const int e = t - c * a.E;
+            const int l0 = c * R;
+            const long long eid = (long long)expert_of_slot[e];
+            const uint32_t rows = (uint32_t)min(R, n_local - l0);
+            const bool scale = lane == 1;
+            const uint32_t rb = scale ? L::kRowSB : L::kRowPB;
+            const uint8_t* src = (scale ? a.w2s + eid * a.strideBs : a.w2p + eid * a.strideBp) +
+                                 (long long)(o_begin + l0) * rb;
+            const uint32_t dst = ring + s * L::kSlotB + (scale ? R * L::kRowPB : 0);
+            const uint32_t bar = bars_b + 8 * s;
+            if (lane == 0) mbar_arrive_expect_tx(bar, rows * (L::kRowPB + L::kRowSB));
+            bulk_copy_g2s(dst, src, rows * rb, bar);
+        }
+    };
+    int tb[SB];
+#pragma unroll
+    for (int s = 0; s < SB; ++s) {
+        tb[s] = claim(&next_task);
+        if (tb[s] < n_tasks && alive) issue_b(tb[s], s);
+    }
+
+    __threadfence();
+    cooperative_groups::this_grid().sync();                          // every SwiGLU row of every expert is written
+
+    // intermediates -> fp16, one scale per expert, once per CTA
+    {
+        constexpr int kPerExpert8 = HT / 8;                          // 8-value chunks per expert
+        constexpr int kEntries = HT / 256;                           // warp-sized groups of chunks per expert
+        constexpr int kPieces = (kRingMaxExperts * kPerExpert8 + NW * 32 - 1) / (NW * 32);
+        const int n8 = a.E * kPerExpert8;
+        float v[kPieces][8];
+#pragma unroll
+        for (int p = 0; p < kPieces; ++p) {
+            const int idx8 = p * NW * 32 + threadIdx.x;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) v[p][i] = 0.f;
+            if (idx8 < n8) load8_as_float(a.mid + (size_t)idx8 * 8, v[p]);
+            uint32_t m = amax_bits8(v[p]);
+#pragma unroll
+            for (int off = 16; off > 0; off >>= 1) m = max(m, __shfl_xor_sync(kFullMask, m, off));
+            if (lane == 0) red[p * NW + warp] = m;                   // entry index = idx8 / 32
+        }
+        __syncthreads();
+#pragma unroll
+        for (int p = 0; p < kPieces; ++p) {
+            const int idx8 = p * NW * 32 + threadIdx.x;
+            if (idx8 < n8) {
+                const int e = idx8 / kPerExpert8;
+                uint32_t m = 0;
+#pragma unroll
+                for (int k = 0; k < kEntries; ++k) m = max(m, red[e * kEntries + k]);
+                float inv;
+                const float sc = fp16_scale_for(m, inv);
+                if (idx8 - e * kPerExpert8 == 0) mid_scale[e] = sc;
+                store8_as_half(vec + (size_t)e * HT, idx8 - e * kPerExpert8, v[p], inv);
+            }
+        }
+        __syncthreads();
+    }
+    // ------------------------------------------------------------------ phase B: down + combine
+    {
+        const uint32_t lane_w = ring + lane * 16;
+        const uint32_t lane_s = ring + R * L::kRowPB + lane;
+        uint32_t parity = 0;
+        for (bool any = true; any; parity ^= 1) {
+            any = false;
+#pragma unroll
+            for (int s = 0; s < SB; ++s) {
+                const int t = tb[s];
+                if (t < n_tasks && alive) {
+                    any = true;
+                    const int c = (int)(((uint32_t)t * inv_e) >> 16);
+                    const int e = t - c * a.E;
+                    const int l0 = c * R;
+                    __half2 m2[L::kBplB][16];
+                    lane_blocks_from_smem<L::kBplB>(vec + (size_t)e * HT, lane, m2);
+                    alive = mbar_wait_bounded(bars_b + 8 * s, parity, 2);
+                    float v[R];
+#pragma unroll
+                    for (int r = 0; r < R; ++r) {
+                        v[r] = 0.f;
+#pragma unroll
+                        for (int j = 0; j < L::kBplB; ++j) {
+                            const uint4 w = lds_v4(lane_w + s * L::kSlotB + r * L::kRowPB + 512 * j);
+                            const float sc = e8m0_to_float_fast(lds_u8(lane_s + s * L::kSlotB + r * L::kRowSB + 32 * j));
+                            v[r] = fmaf(fp4_block_dot(w, m2[j]), sc, v[r]);
+                        }
+                    }
+                    multi_reduce<R>(v, lane);
+                    if (multi_reduce_owner<R>(lane) && alive) {
+                        const int l = l0 + multi_reduce_index<R>(lane);
+                        if (l < n_local) part[l][e] = v[0] * mid_scale[e];   // rows past the chunk hold stale bytes
+                    }
+                    __syncwarp();                                    // every lane has read the slot
+                    tb[s] = claim(&next_task);
+                    if (tb[s] < n_tasks && alive) issue_b(tb[s], s);
+                }
+            }
+        }
+    }
+    __syncthreads();
+
+    for (int t = threadIdx.x; t < n_local; t += blockDim.x) {
+        float acc = 0.f;
+        for (int k = 0; k < a.E; ++k) acc = fmaf(weight_of_slot[k], part[t][k], acc);
+        a.out[o_begin + t] = __float2bfloat16(acc);
+    }
+}
+
+}  // namespace dsv4

@@ -163,7 +163,6 @@ __global__ void __launch_bounds__(kRingGateWarps * 32, 1) gate_up_ring_kernel(co
     };
 
     // stacked weights do not depend on the previous kernel in the stream: request them before waiting for it
-#ifndef DSV4_EXP_NOLOAD
     if (!use_table) prologue();
     pdl_wait();
     if (use_table) {
@@ -185,7 +184,6 @@ __global__ void __launch_bounds__(kRingGateWarps * 32, 1) gate_up_ring_kernel(co
         __syncthreads();
         prologue();
     }
-#endif
 
     // x -> fp16 with one scale, once per CTA
     float xs;
@@ -218,11 +216,8 @@ __global__ void __launch_bounds__(kRingGateWarps * 32, 1) gate_up_ring_kernel(co
         for (int s = 0; s < S; ++s) {
             const int i = i0 + s;
             if (i < n_i && alive) {
-#ifndef DSV4_EXP_NOLOAD
                 alive = mbar_wait_bounded(bars + 8 * s, parity, 1);
-#endif
                 float v[2] = {0.f, 0.f};
-#ifndef DSV4_EXP_NOCOMPUTE
 #pragma unroll
                 for (int j = 0; j < BPL; ++j) {
                     const uint4 wg = lds_v4(lane_w + s * L::kSlot + 512 * j);
@@ -232,7 +227,6 @@ __global__ void __launch_bounds__(kRingGateWarps * 32, 1) gate_up_ring_kernel(co
                     v[0] = fmaf(fp4_block_dot(wg, x[j]), sg, v[0]);
                     v[1] = fmaf(fp4_block_dot(wu, x[j]), su, v[1]);
                 }
-#endif
                 multi_reduce<2>(v, lane);                            // lane 0: gate sum, lane 16: up sum
                 const float up = __shfl_sync(kFullMask, v[0], 16) * xs;
                 if (lane == 0 && alive) {
@@ -240,9 +234,7 @@ __global__ void __launch_bounds__(kRingGateWarps * 32, 1) gate_up_ring_kernel(co
                     a.mid[q0 + i * NW] = (g / (1.0f + __expf(-g))) * up;
                 }
                 __syncwarp();                                        // every lane has read the slot
-#ifndef DSV4_EXP_NOLOAD
                 if (i + S < n_i && alive) issue(q0 + (i + S) * NW, s);
-#endif
             }
         }
     }
@@ -318,16 +310,13 @@ __global__ void __launch_bounds__(2 * kRingMaxExperts * 32, 1) down_ring_kernel(
             if (s < n_i) issue(half + 2 * s, s);
     };
 
-#ifndef DSV4_EXP_NOLOAD
     if (a.ids == nullptr) prologue();
     pdl_wait();
     if (a.ids != nullptr) { eid = a.ids[e]; prologue(); }
-#endif
 
     // SwiGLU intermediate of this warp's expert -> fp16 with one scale per expert; the expert's two warps
     // convert half of it each
     float ms = 1.f;
-#ifndef DSV4_EXP_NOSTAGE
     {
         // the expert's two warps (64 lanes) read the vector in coalesced 32-byte pieces: piece p of a lane covers
         // values 8 * (p * 64 + half * 32 + lane) ..., kept in registers between the two steps
@@ -351,13 +340,8 @@ __global__ void __launch_bounds__(2 * kRingMaxExperts * 32, 1) down_ring_kernel(
         for (int p = 0; p < kPieces; ++p) store8_as_half(mh + (size_t)e * HT, p * 64 + half * 32 + lane, v[p], inv);
         __syncthreads();
     }
-#endif
     __half2 m2[BPL][16];
-#ifndef DSV4_EXP_NOSMEMX
     lane_blocks_from_smem<BPL>(mh + (size_t)e * HT, lane, m2);
-#else
-    for (int j = 0; j < BPL; ++j) for (int c = 0; c < 16; ++c) m2[j][c] = __float2half2_rn(1.0f + lane);
-#endif
 
     const uint32_t lane_w = ring + lane * 16;
     const uint32_t lane_s = ring + R * L::kRowP + lane;
@@ -368,22 +352,18 @@ __global__ void __launch_bounds__(2 * kRingMaxExperts * 32, 1) down_ring_kernel(
         for (int s = 0; s < S; ++s) {
             const int i = i0 + s;
             if (i < n_i && alive) {
-#ifndef DSV4_EXP_NOLOAD
                 alive = mbar_wait_bounded(bars + 8 * s, parity, 2);
-#endif
                 const int l0 = (half + 2 * i) * R;
                 float v[R];
 #pragma unroll
                 for (int r = 0; r < R; ++r) {
                     v[r] = 0.f;
-#ifndef DSV4_EXP_NOCOMPUTE
 #pragma unroll
                     for (int j = 0; j < BPL; ++j) {
                         const uint4 w = lds_v4(lane_w + s * L::kSlot + r * L::kRowP + 512 * j);
                         const float sc = e8m0_to_float_fast(lds_u8(lane_s + s * L::kSlot + r * L::kRowS + 32 * j));
                         v[r] = fmaf(fp4_block_dot(w, m2[j]), sc, v[r]);
                     }
-#endif
                 }
                 multi_reduce<R>(v, lane);
                 if (multi_reduce_owner<R>(lane) && alive) {
@@ -391,9 +371,7 @@ __global__ void __launch_bounds__(2 * kRingMaxExperts * 32, 1) down_ring_kernel(
                     if (l < n_local) part[l][e] = v[0] * ms;        // rows past the chunk's end hold stale bytes
                 }
                 __syncwarp();                                        // every lane has read the slot
-#ifndef DSV4_EXP_NOLOAD
                 if (i + S < n_i && alive) issue(half + 2 * (i + S), s);
-#endif
             }
         }
     }

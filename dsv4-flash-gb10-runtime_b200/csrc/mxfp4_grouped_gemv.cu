@@ -21,6 +21,7 @@
 #include "grouped_args.cuh"
 #include "router.cuh"
 #include "grouped_ring.cuh"
+#include "decode_fused.cuh"
 
 #include <cstdio>
 #include <cstdlib>
@@ -351,6 +352,64 @@ static cudaError_t allow_smem(Kernel kernel, size_t bytes, int (&done)[64]) {
     return err;
 }
 
+static bool fused_enabled() {
+    static int v = -1;
+    if (v < 0) {
+        const char* e = std::getenv("DSV4_B200_FUSED");
+        v = (e && e[0] == '0') ? 0 : 1;
+    }
+    return v == 1;
+}
+
+// Single persistent kernel (decode_fused.cuh), launched cooperatively with one CTA per SM.
+// Returns 1 when it cannot be used here (the caller then launches the two chained kernels).
+template <int KT, int HT>
+static int grouped_launch_fused(const GroupedArgs& a, cudaStream_t stream, int h_shift, const RouteArgs& rt) {
+    static int done[64] = {0};
+    static int coop_ctas[64] = {0};      // resident CTAs per device for this kernel; -1 = cooperative launch unusable
+    using L = FusedLayout<KT, HT>;
+    auto kernel = moe_decode_fused_kernel<KT, HT>;
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 1;
+    if (coop_ctas[dev] == 0) {
+        int coop = 0, per_sm = 0;
+        cudaDeviceGetAttribute(&coop, cudaDevAttrCooperativeLaunch, dev);
+        if (allow_smem(kernel, L::kBytes, done) != cudaSuccess || !coop ||
+            cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, kFusedWarps * 32, L::kBytes) != cudaSuccess ||
+            per_sm < 1) {
+            cudaGetLastError();
+            coop_ctas[dev] = -1;
+        } else {
+            coop_ctas[dev] = sm_count();     // one CTA per SM
+        }
+    }
+    if (coop_ctas[dev] < 0) return 1;
+    long long grid = coop_ctas[dev];
+    const long long pairs = (long long)a.E * a.H;
+    if (grid > pairs) grid = pairs;
+    if (grid > a.O) grid = a.O;
+    if ((long long)kFusedCap * grid < a.O) return 1;                 // too many output rows per CTA
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)grid);
+    cfg.blockDim = dim3(kFusedWarps * 32);
+    cfg.dynamicSmemBytes = L::kBytes;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[2];
+    attr[0].id = cudaLaunchAttributeCooperative;
+    attr[0].val.cooperative = 1;
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;        // a cooperative launch is not combined with programmatic stream serialisation
+    const cudaError_t err = cudaLaunchKernelEx(&cfg, kernel, a, h_shift, rt);
+    if (err != cudaSuccess) {
+        cudaGetLastError();
+        coop_ctas[dev] = -1;                                         // do not try again on this device
+        return 1;
+    }
+    return 0;
+}
+
 // Shared-memory ring path (grouped_ring.cuh).  Returns 1 when the shape is not one it serves.
 template <int KT, int HT>
 static int grouped_launch_ring(const GroupedArgs& a, cudaStream_t stream, const char* who, int h_shift,
@@ -398,7 +457,11 @@ static int grouped_try_ring(const GroupedArgs& a, cudaStream_t stream, const cha
         return 1;
     int h_shift = 0;
     while ((1 << h_shift) < a.H) ++h_shift;
-#define DSV4_RING(KT, HT) if (a.K == KT && a.H == HT) return grouped_launch_ring<KT, HT>(a, stream, who, h_shift, stages, rt);
+#define DSV4_RING(KT, HT)                                                                          \
+    if (a.K == KT && a.H == HT) {                                                                  \
+        if (stages == 3 && fused_enabled() && grouped_launch_fused<KT, HT>(a, stream, h_shift, rt) == 0) return 0; \
+        return grouped_launch_ring<KT, HT>(a, stream, who, h_shift, stages, rt);                  \
+    }
     DSV4_RING(4096, 2048) DSV4_RING(4096, 1024) DSV4_RING(2048, 2048) DSV4_RING(2048, 1024)
     DSV4_RING(1024, 2048) DSV4_RING(1024, 1024)
 #undef DSV4_RING
