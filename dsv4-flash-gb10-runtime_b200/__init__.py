@@ -7,7 +7,7 @@ The directory name carries a hyphen, so it cannot be imported by name; load it w
 Layout
 ------
 csrc/      CUDA sources of the three shared libraries (Makefile in this directory builds them into lib/)
-lib/       built libraries: libmxfp4_grouped_gemv.so, libmxfp4_gemv.so, libfp8_e4m3_gemv.so
+lib/       built libraries: libmxfp4_grouped_gemv.so, libmxfp4_gemv.so, libfp8_e4m3_gemv.so, libmxfp4_moe.so
 runtime/   host-side mirror of the reference's ctypes bindings (same function names and argument meaning),
            plus the routed-expert bank / router / expert-parallel helpers
 
@@ -25,6 +25,7 @@ LIB_FILES = {
     "grouped": "libmxfp4_grouped_gemv.so",
     "mxfp4": "libmxfp4_gemv.so",
     "fp8": "libfp8_e4m3_gemv.so",
+    "moe": "libmxfp4_moe.so",
 }
 
 # Same override variables as the reference's bindings (runtime/mxfp4_grouped_gemv_binding.py:31-36,
@@ -33,6 +34,7 @@ LIB_ENV = {
     "grouped": "MXFP4_GROUPED_LIB",
     "mxfp4": "MXFP4_GEMV_LIB",
     "fp8": "FP8_E4M3_GEMV_LIB",
+    "moe": "MXFP4_MOE_LIB",
 }
 
 

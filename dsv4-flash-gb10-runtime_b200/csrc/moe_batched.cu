@@ -1,0 +1,162 @@
+// libmxfp4_moe.so — routed-expert MXFP4 MoE layer for a BATCH of tokens on B200 (sm_100a): batched decode and
+// prefill.  No counterpart in the reference (its path is one token at a time,
+// runtime/dsv4_engine_mxfp4.py:412-422 loops tokens); the arithmetic contract is the same FFN:
+//   out[t] = sum_j w[t, j] * W2_e ( silu(W1_e x_t) * (W3_e x_t) ),  e = ids[t, j].
+// Pipeline on the caller's stream: tokens -> normalised fp16; pairs grouped by expert; grouped GEMM 1 (gate/up +
+// SwiGLU) and grouped GEMM 2 (down, router weight applied) on tcgen05 tensor cores (moe_gemm_kernel.cuh);
+// per-token sum in the router's order.  Nothing is allocated; all scratch lives in the caller's workspace.
+#include "moe_gemm_kernel.cuh"
+
+#include <cstdio>
+#include <cstdlib>
+
+using namespace dsv4;
+
+namespace {
+
+struct Carve {
+    size_t off = 0;
+    size_t take(size_t bytes) { const size_t at = off; off += (bytes + 255) & ~size_t(255); return at; }
+};
+
+struct WorkspaceMap {
+    size_t xh, xexp, offsets, tiles_up, tiles_down, slot_pair, pair_slot, mid, y, total;
+};
+
+WorkspaceMap map_workspace(long long T, int k, int K, int H, int O, int E) {
+    const long long P = T * k;
+    Carve c;
+    WorkspaceMap m;
+    m.xh = c.take((size_t)T * K * 2);
+    m.xexp = c.take((size_t)T * 4);
+    m.offsets = c.take((size_t)(E + 1) * 4);
+    m.tiles_up = c.take((size_t)(E + 1) * 4);
+    m.tiles_down = c.take((size_t)(E + 1) * 4);
+    m.slot_pair = c.take((size_t)P * 4);
+    m.pair_slot = c.take((size_t)P * 4);
+    m.mid = c.take((size_t)P * H * 2);
+    m.y = c.take((size_t)P * O * 4);
+    m.total = c.off;
+    return m;
+}
+
+int sm_count() {
+    static int cached[64] = {0};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 148;
+    if (cached[dev] == 0) {
+        int n = 0;
+        if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+        cached[dev] = n;
+    }
+    return cached[dev];
+}
+
+template <class Kernel>
+cudaError_t allow_smem(Kernel kernel, size_t bytes, int (&done)[64]) {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) dev = 0;
+    if (done[dev] >= (int)bytes) return cudaSuccess;
+    cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
+    if (err == cudaSuccess) done[dev] = (int)bytes;
+    return err;
+}
+
+bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+}  // namespace
+
+// Bytes of workspace mxfp4_moe_forward needs (normalised activations, grouping tables, the fp16 intermediate
+// [n_tokens * k, hidden] and the FP32 per-pair outputs [n_tokens * k, out_dim]).
+DSV4_API size_t mxfp4_moe_forward_workspace_bytes(int n_tokens, int k, int K_in, int hidden, int out_dim,
+                                                  int n_experts) {
+    if (n_tokens <= 0 || k <= 0 || K_in <= 0 || hidden <= 0 || out_dim <= 0 || n_experts <= 0) return 0;
+    return map_workspace(n_tokens, k, K_in, hidden, out_dim, n_experts).total;
+}
+
+// x bf16 [n_tokens, K_in]; bank tensors stacked over n_experts as in mxfp4_grouped_gemv_topk_ids; ids int32
+// [n_tokens, k] (a token lists an expert at most once), weights FP32 [n_tokens, k]; out bf16 [n_tokens, out_dim].
+// Shapes: K_in and hidden multiples of 256, hidden and out_dim multiples of 128, n_experts <= 1024.
+// Returns 0, -1 bad shape, -2 null / misaligned pointer, -3 launch failure.
+DSV4_API int mxfp4_moe_forward(const __nv_bfloat16* x, const uint8_t* bank_W1_packed, const uint8_t* bank_W3_packed,
+                               const uint8_t* bank_W2_packed, const uint8_t* bank_W1_scale,
+                               const uint8_t* bank_W3_scale, const uint8_t* bank_W2_scale, const int* ids,
+                               const float* weights, int n_tokens, int n_experts, int K_in, int hidden, int out_dim,
+                               int k, __nv_bfloat16* out, void* workspace, cudaStream_t stream) {
+    const char* who = "mxfp4_moe_forward";
+    if (n_tokens < 0 || k <= 0 || n_experts <= 0 || n_experts > kMoeMaxExperts || K_in <= 0 || K_in % 256 != 0 ||
+        hidden <= 0 || hidden % 256 != 0 || out_dim <= 0 || out_dim % 128 != 0 || K_in > 16384 || hidden > 16384) {
+        std::fprintf(stderr, "%s: unsupported shape T=%d E=%d K=%d H=%d O=%d k=%d\n", who, n_tokens, n_experts, K_in,
+                     hidden, out_dim, k);
+        return -1;
+    }
+    if (n_tokens == 0) return 0;
+    if (!x || !bank_W1_packed || !bank_W3_packed || !bank_W2_packed || !bank_W1_scale || !bank_W3_scale ||
+        !bank_W2_scale || !ids || !weights || !out || !workspace || !aligned16(x) || !aligned16(bank_W1_packed) ||
+        !aligned16(bank_W3_packed) || !aligned16(bank_W2_packed) || !aligned16(bank_W1_scale) ||
+        !aligned16(bank_W3_scale) || !aligned16(bank_W2_scale) || !aligned16(workspace) || !aligned16(out)) {
+        std::fprintf(stderr, "%s: null pointer or a tensor that is not 16-byte aligned\n", who);
+        return -2;
+    }
+    static int up_done[64] = {0}, down_done[64] = {0};
+    uint8_t* ws = reinterpret_cast<uint8_t*>(workspace);
+    const WorkspaceMap m = map_workspace(n_tokens, k, K_in, hidden, out_dim, n_experts);
+    const int P = n_tokens * k;
+    MoeGroups g;
+    g.offsets = reinterpret_cast<int*>(ws + m.offsets);
+    g.tiles_up = reinterpret_cast<int*>(ws + m.tiles_up);
+    g.tiles_down = reinterpret_cast<int*>(ws + m.tiles_down);
+    g.slot_pair = reinterpret_cast<int*>(ws + m.slot_pair);
+    g.pair_slot = reinterpret_cast<int*>(ws + m.pair_slot);
+    __half* xh = reinterpret_cast<__half*>(ws + m.xh);
+    int* xexp = reinterpret_cast<int*>(ws + m.xexp);
+    __half* mid = reinterpret_cast<__half*>(ws + m.mid);
+    float* y = reinterpret_cast<float*>(ws + m.y);
+
+    int* status = nullptr;
+    cudaGetSymbolAddress(reinterpret_cast<void**>(&status), g_device_status);
+    moe_token_fp16_kernel<<<(n_tokens + 7) / 8, 256, 0, stream>>>(x, n_tokens, K_in, xh, xexp);
+    moe_group_kernel<<<1, 1024, 0, stream>>>(ids, P, n_experts, hidden, out_dim, g, status);
+
+    const int grid = sm_count();
+    MoeGemmArgs up;
+    up.wa_p = bank_W1_packed; up.wb_p = bank_W3_packed; up.wa_s = bank_W1_scale; up.wb_s = bank_W3_scale;
+    up.stride_p = (long long)hidden * (K_in / 2); up.stride_s = (long long)hidden * (K_in / 32);
+    up.rows = hidden; up.K = K_in; up.n_experts = n_experts; up.k_top = k;
+    up.act = xh; up.xexp = xexp; up.pair_w = weights; up.g = g; up.mid = mid; up.y = nullptr;
+    const size_t smem_up = MoeGemmLayout<0>::bytes(K_in);
+    cudaError_t err = allow_smem(moe_gemm_kernel<0>, smem_up, up_done);
+    if (err == cudaSuccess) {
+        moe_gemm_kernel<0><<<grid, kGemmThreads, smem_up, stream>>>(up);
+        err = cudaGetLastError();
+    }
+    MoeGemmArgs down = up;
+    down.wa_p = bank_W2_packed; down.wb_p = nullptr; down.wa_s = bank_W2_scale; down.wb_s = nullptr;
+    down.stride_p = (long long)out_dim * (hidden / 2); down.stride_s = (long long)out_dim * (hidden / 32);
+    down.rows = out_dim; down.K = hidden; down.act = mid; down.mid = nullptr; down.y = y;
+    const size_t smem_down = MoeGemmLayout<1>::bytes(hidden);
+    if (err == cudaSuccess) err = allow_smem(moe_gemm_kernel<1>, smem_down, down_done);
+    if (err == cudaSuccess) {
+        moe_gemm_kernel<1><<<grid, kGemmThreads, smem_down, stream>>>(down);
+        err = cudaGetLastError();
+    }
+    if (err == cudaSuccess) {
+        dim3 cgrid((out_dim / 4 + 127) / 128, n_tokens);
+        moe_combine_kernel<<<cgrid, 128, 0, stream>>>(y, g.pair_slot, n_tokens, k, out_dim, out);
+        err = cudaGetLastError();
+    }
+    if (err != cudaSuccess) {
+        std::fprintf(stderr, "%s: launch failed: %s\n", who, cudaGetErrorString(err));
+        return -3;
+    }
+    return 0;
+}
+
+// 0 unless a kernel of this library gave up on a bounded wait (4 producer, 5 MMA issuer, 6 epilogue) or met an
+// expert id outside the bank (3) since the last call; clears the status.  Synchronises the device.
+DSV4_API int mxfp4_moe_device_status(void) {
+    int v = 0, zero = 0;
+    if (cudaMemcpyFromSymbol(&v, g_device_status, sizeof(int)) != cudaSuccess) return -1;
+    if (v != 0) cudaMemcpyToSymbol(g_device_status, &zero, sizeof(int));
+    return v;
+}

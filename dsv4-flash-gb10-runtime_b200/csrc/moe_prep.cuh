@@ -1,0 +1,120 @@
+// Small kernels around the batched routed-expert GEMMs: activations to normalised fp16, grouping of
+// (token, expert) pairs by expert, and the final per-token sum.
+#pragma once
+
+#include "gemv_engine.cuh"
+
+namespace dsv4 {
+
+constexpr int kMoeMaxExperts = 1024;
+constexpr int kMoeTileRows = 128;      // weight rows per tensor-core tile (the MMA's M)
+constexpr int kMoeTileTokens = 128;    // tokens per tile at most (the MMA's N)
+
+// Work descriptors written by the grouping kernel, read by the GEMM kernels.
+struct MoeGroups {
+    int* offsets;        // [E + 1] first slot of every expert (slots = pairs sorted by expert)
+    int* tiles_up;       // [E + 1] prefix sum of gate/up tiles per expert
+    int* tiles_down;     // [E + 1] prefix sum of down tiles per expert
+    int* slot_pair;      // [P] slot -> pair index t * k + j
+    int* pair_slot;      // [P] pair index -> slot
+};
+
+// One warp per token: x (bf16) -> x * 2^-e as fp16 with the largest magnitude in [1, 2), e stored per token.
+// Rows of all-zero tokens get e = 0.
+__global__ void moe_token_fp16_kernel(const __nv_bfloat16* __restrict__ x, int n_tokens, int K,
+                                      __half* __restrict__ xh, int* __restrict__ xexp) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int lane = threadIdx.x & 31;
+    const int t = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (t >= n_tokens) return;
+    const __nv_bfloat16* row = x + (size_t)t * K;
+    uint32_t m = 0;
+    for (int c = lane; c < K / 8; c += 32) {
+        float v[8];
+        load8_as_float(row + 8 * c, v);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) m = max(m, __float_as_uint(v[i]) & 0x7fffffffu);
+    }
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) m = max(m, __shfl_xor_sync(kFullMask, m, off));
+    int e = (int)(m >> 23) - 127;                      // floor(log2(amax)); -127 for zero / subnormal rows
+    if (m == 0) e = 0;
+    e = min(max(e, -100), 100);
+    const float inv = __uint_as_float((uint32_t)(127 - e) << 23);
+    for (int c = lane; c < K / 8; c += 32) {
+        float v[8];
+        load8_as_float(row + 8 * c, v);
+        __half2 h[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) h[i] = __floats2half2_rn(v[2 * i] * inv, v[2 * i + 1] * inv);
+        *reinterpret_cast<uint4*>(xh + (size_t)t * K + 8 * c) = *reinterpret_cast<const uint4*>(h);
+    }
+    if (lane == 0) xexp[t] = e;
+}
+
+// Single CTA: counting sort of the P = n_tokens * k pairs by expert id.  The order of pairs inside an expert is
+// arbitrary (it only decides which accumulator column a token uses, not any arithmetic).
+__global__ void __launch_bounds__(1024) moe_group_kernel(const int* __restrict__ ids, int n_pairs, int n_experts,
+                                                         int rows_up, int rows_down, MoeGroups g,
+                                                         int* __restrict__ status) {
+    __shared__ int count[kMoeMaxExperts];
+    __shared__ int cursor[kMoeMaxExperts];
+    pdl_launch_dependents();
+    pdl_wait();
+    for (int e = threadIdx.x; e < n_experts; e += blockDim.x) count[e] = 0;
+    __syncthreads();
+    for (int p = threadIdx.x; p < n_pairs; p += blockDim.x) {
+        const int e = ids[p];
+        if (e >= 0 && e < n_experts) atomicAdd(&count[e], 1);
+        else atomicExch(status, 3);                      // expert id out of range: the pair is dropped
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        int off = 0, tu = 0, td = 0;
+        for (int e = 0; e < n_experts; ++e) {
+            g.offsets[e] = off; g.tiles_up[e] = tu; g.tiles_down[e] = td;
+            cursor[e] = off;
+            const int n_tiles = (count[e] + kMoeTileTokens - 1) / kMoeTileTokens;
+            off += count[e];
+            tu += n_tiles * (rows_up / kMoeTileRows);
+            td += n_tiles * (rows_down / kMoeTileRows);
+        }
+        g.offsets[n_experts] = off; g.tiles_up[n_experts] = tu; g.tiles_down[n_experts] = td;
+    }
+    __syncthreads();
+    for (int p = threadIdx.x; p < n_pairs; p += blockDim.x) {
+        const int e = ids[p];
+        if (e >= 0 && e < n_experts) {
+            const int slot = atomicAdd(&cursor[e], 1);
+            g.slot_pair[slot] = p;
+            g.pair_slot[p] = slot;
+        } else {
+            g.pair_slot[p] = -1;
+        }
+    }
+}
+
+// out[t, :] = bf16( sum_j y[slot(t, j), :] ), j in the router's order (fixed summation order).
+__global__ void moe_combine_kernel(const float* __restrict__ y, const int* __restrict__ pair_slot, int n_tokens,
+                                   int k, int O, __nv_bfloat16* __restrict__ out) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int t = blockIdx.y;
+    const int o = (blockIdx.x * blockDim.x + threadIdx.x) * 4;
+    if (t >= n_tokens || o >= O) return;
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int j = 0; j < k; ++j) {
+        const int slot = pair_slot[t * k + j];
+        if (slot < 0) continue;
+        const float4 v = __ldcs(reinterpret_cast<const float4*>(y + (size_t)slot * O + o));
+        acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+    }
+    __nv_bfloat162 lo = __floats2bfloat162_rn(acc.x, acc.y), hi = __floats2bfloat162_rn(acc.z, acc.w);
+    uint2 packed;
+    packed.x = *reinterpret_cast<uint32_t*>(&lo);
+    packed.y = *reinterpret_cast<uint32_t*>(&hi);
+    *reinterpret_cast<uint2*>(out + (size_t)t * O + o) = packed;
+}
+
+}  // namespace dsv4

@@ -4,3 +4,4 @@ from .fp8_e4m3_gemv_binding import fp8_e4m3_gemv, fp8_e4m3_gemv_f32scale     # n
 from .mxfp4_grouped_gemv_binding import (                                    # noqa: F401
     mxfp4_grouped_gemv, mxfp4_grouped_gemv_static, mxfp4_grouped_gemv_ids, mxfp4_dequant_bf16, moe_route_topk, device_status,
     moe_decode_layer, decode_workspace_bytes, decode_picks)
+from .moe_batched import moe_forward, forward_workspace_bytes, moe_device_status   # noqa: F401

@@ -26,6 +26,11 @@ SIGNATURES = {
     "mxfp4": {
         "mxfp4_gemv_m1": (c_int, [_P, _P, _P, c_int, c_int, c_int64, c_int64, _P, _P]),
     },
+    "moe": {
+        "mxfp4_moe_forward": (c_int, [_P] * 9 + [c_int] * 6 + [_P, _P, _P]),
+        "mxfp4_moe_forward_workspace_bytes": (c_size_t, [c_int] * 6),
+        "mxfp4_moe_device_status": (c_int, []),
+    },
     "fp8": {
         "fp8_e4m3_gemv_m1": (c_int, [_P, _P, _P, c_int, c_int, c_int64, c_int64, _P, _P]),
         "fp8_e4m3_gemv_m1_f32scale": (c_int, [_P, _P, _P, c_int, c_int, c_int64, c_int64, _P, _P]),

@@ -1,0 +1,55 @@
+"""Routed-expert MoE layer for a batch of tokens (batched decode, prefill) on the tcgen05 tensor cores.
+
+    out = moe_forward(bank, x, ids, weights)
+
+bank: dict of 'w1p','w3p' uint8 [E, hidden, K/2], 'w2p' [E, out_dim, hidden/2] and the E8M0 scales 'w1s','w3s','w2s';
+x bfloat16 [T, K]; ids int32 [T, k] (a token lists an expert at most once); weights float32 [T, k].
+Returns bfloat16 [T, out_dim].  The reference has no batched path (it loops tokens,
+runtime/dsv4_engine_mxfp4.py:412-422); the result is the same per-token FFN sum.
+"""
+from __future__ import annotations
+
+from ctypes import c_int
+from typing import Dict, Optional
+
+import torch
+
+from . import _capi
+
+
+def forward_workspace_bytes(n_tokens: int, k: int, K_in: int, hidden: int, out_dim: int, n_experts: int) -> int:
+    return int(_capi.load("moe").mxfp4_moe_forward_workspace_bytes(n_tokens, k, K_in, hidden, out_dim, n_experts))
+
+
+def moe_forward(bank: Dict[str, torch.Tensor], x: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor,
+                out: Optional[torch.Tensor] = None, workspace: Optional[torch.Tensor] = None) -> torch.Tensor:
+    lib = _capi.load("moe")
+    for name, t, dt in (("x", x, torch.bfloat16), ("ids", ids, torch.int32), ("weights", weights, torch.float32)):
+        if not t.is_cuda or t.dtype != dt or not t.is_contiguous():
+            raise ValueError(f"{name}: expected a contiguous CUDA tensor of {dt}")
+    T, K = x.shape
+    k = ids.shape[1]
+    E, hidden, out_dim = bank["w1p"].shape[0], bank["w1p"].shape[1], bank["w2p"].shape[1]
+    if tuple(ids.shape) != (T, k) or tuple(weights.shape) != (T, k):
+        raise ValueError("ids / weights must be [T, k]")
+    if bank["w1p"].shape[2] != K // 2 or bank["w2p"].shape[2] != hidden // 2:
+        raise ValueError("bank shapes do not match x")
+    if out is None:
+        out = torch.empty(T, out_dim, dtype=torch.bfloat16, device=x.device)
+    if workspace is None:
+        workspace = torch.empty(forward_workspace_bytes(T, k, K, hidden, out_dim, E), dtype=torch.uint8, device=x.device)
+    rc = lib.mxfp4_moe_forward(_capi.ptr(x), _capi.ptr(bank["w1p"]), _capi.ptr(bank["w3p"]), _capi.ptr(bank["w2p"]),
+                               _capi.ptr(bank["w1s"]), _capi.ptr(bank["w3s"]), _capi.ptr(bank["w2s"]), _capi.ptr(ids),
+                               _capi.ptr(weights), c_int(T), c_int(E), c_int(K), c_int(hidden), c_int(out_dim), c_int(k),
+                               _capi.ptr(out), _capi.ptr(workspace), _capi.stream_ptr(x.device))
+    if rc != 0:
+        raise RuntimeError(f"mxfp4_moe_forward returned {rc}")
+    return out
+
+
+def moe_device_status() -> int:
+    """0 unless a kernel of the batched library gave up on a bounded wait or met a bad expert id (synchronises)."""
+    return int(_capi.load("moe").mxfp4_moe_device_status())
+
+
+__all__ = ["moe_forward", "forward_workspace_bytes", "moe_device_status"]

@@ -123,6 +123,21 @@ int fp8_e4m3_gemv_m1_f32scale(const uint16_t* x, const uint8_t* W_fp8, const flo
                               int64_t weight_row_stride_bytes, int64_t scale_row_stride_bytes, uint16_t* y,
                               void* stream);
 
+/* ---- libmxfp4_moe.so (added; no counterpart: the reference runs one token at a time) ---------------------- */
+
+/* Routed-expert MoE layer for a batch of tokens on the tensor cores: out[t] = sum_j weights[t,j] * FFN_{ids[t,j]}(x[t]).
+ * x bf16 [n_tokens, K_in]; bank tensors as in mxfp4_grouped_gemv_topk_ids; ids int32 [n_tokens, k]; weights FP32
+ * [n_tokens, k]; out bf16 [n_tokens, out_dim].  K_in, hidden multiples of 256; out_dim multiple of 128;
+ * n_experts <= 1024.  Returns -1 bad shape, -2 null / misaligned pointer, -3 launch failure. */
+int mxfp4_moe_forward(const uint16_t* x, const uint8_t* bank_W1_packed, const uint8_t* bank_W3_packed,
+                      const uint8_t* bank_W2_packed, const uint8_t* bank_W1_scale, const uint8_t* bank_W3_scale,
+                      const uint8_t* bank_W2_scale, const int* ids, const float* weights, int n_tokens, int n_experts,
+                      int K_in, int hidden, int out_dim, int k, uint16_t* out, void* workspace, void* stream);
+size_t mxfp4_moe_forward_workspace_bytes(int n_tokens, int k, int K_in, int hidden, int out_dim, int n_experts);
+/* 0, or the code a kernel of this library recorded since the last call (3 bad expert id, 4/5/6 a bounded wait ran
+ * out); clears it.  Synchronises the device. */
+int mxfp4_moe_device_status(void);
+
 #ifdef __cplusplus
 }
 #endif

@@ -183,7 +183,8 @@ def fp8_gemv_ref(w_bytes, scale_bytes, x_bf16: torch.Tensor) -> np.ndarray:
 
 def _silu(v: np.ndarray) -> np.ndarray:
     v = v.astype(np.float32)
-    return v / (1.0 + np.exp(-v, dtype=np.float32))
+    with np.errstate(over="ignore"):      # exp(+large) -> inf -> v / inf = -0.0, the right limit
+        return v / (1.0 + np.exp(-v, dtype=np.float32))
 
 
 def grouped_gemv_ref(x_bf16, w1p, w3p, w2p, w1s, w3s, w2s, r) -> np.ndarray:
