@@ -160,3 +160,10 @@ DSV4_API int mxfp4_moe_device_status(void) {
     if (v != 0) cudaMemcpyToSymbol(g_device_status, &zero, sizeof(int));
     return v;
 }
+
+#ifdef DSV4_EXP_PROF
+DSV4_API void mxfp4_moe_prof(long long* out64, int reset) {
+    cudaMemcpyFromSymbol(out64, g_prof, sizeof(long long) * 64);
+    if (reset) { long long z[64] = {0}; cudaMemcpyToSymbol(g_prof, z, sizeof(z)); }
+}
+#endif

@@ -15,8 +15,8 @@
 //     product of two dot products of normalised activations with weight rows, whatever the scale of x.
 // The powers of two are multiplied back in the epilogues, in FP32.
 //
-// CTA = 9 warps: warps 0..7 dequantise the weight tiles and copy the token tile into a ring of shared-memory
-// stages (K-major, 128-byte swizzle), one lane of warp 8 issues the MMAs and releases stages through
+// CTA = 17 warps: warps 0..15 dequantise the weight tiles and copy the token tile into a ring of shared-memory
+// stages (K-major, 128-byte swizzle), one lane of warp 16 issues the MMAs and releases stages through
 // tcgen05.commit; warps 0..3 then read the accumulators.  Persistent grid, one CTA per SM, static tile striding.
 // Every wait is bounded (stream_ring.cuh).
 #pragma once
@@ -27,8 +27,8 @@
 
 namespace dsv4 {
 
-constexpr int kGemmThreads = 288;
-constexpr int kGemmProducers = 256;
+constexpr int kGemmProducers = 512;             // 16 producer warps
+constexpr int kGemmThreads = kGemmProducers + 32;
 constexpr int kGemmKBlock = 64;                 // K values per stage (128 bytes of fp16 per row)
 constexpr uint32_t kGemmTileBytes = 128 * 128;  // one operand tile of 128 rows
 

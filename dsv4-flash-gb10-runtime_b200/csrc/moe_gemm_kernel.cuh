@@ -5,6 +5,13 @@
 
 namespace dsv4 {
 
+#ifdef DSV4_EXP_PROF
+__device__ long long g_prof[64];
+#define PROF_ADD(i, v) do { if (blockIdx.x == 0 && lane == 0) atomicAdd((unsigned long long*)&g_prof[(i)], (unsigned long long)(v)); } while (0)
+#else
+#define PROF_ADD(i, v) do { } while (0)
+#endif
+
 template <int MODE>
 __global__ void __launch_bounds__(kGemmThreads, 1) moe_gemm_kernel(const MoeGemmArgs a) {
     using L = MoeGemmLayout<MODE>;
@@ -20,14 +27,15 @@ __global__ void __launch_bounds__(kGemmThreads, 1) moe_gemm_kernel(const MoeGemm
     pdl_launch_dependents();
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const bool producer = warp < 8;
+    constexpr int kProducerWarps = kGemmProducers / 32;
+    const bool producer = warp < kProducerWarps;
     const int n_kb = a.K / kGemmKBlock;
     const int scale_row = a.K / 32;          // scale bytes per weight row
     uint8_t* scale_cache = gemm_smem + L::kScaleCache;
 
-    if (warp == 8) tc05_alloc(smem_u32(&tmem_holder), 256);
+    if (warp == kProducerWarps) tc05_alloc(smem_u32(&tmem_holder), 256);
     if (tid == 0) {
-        for (int s = 0; s < S; ++s) { mbar_init(smem_u32(&bar_full[s]), 8); mbar_init(smem_u32(&bar_empty[s]), 1); }
+        for (int s = 0; s < S; ++s) { mbar_init(smem_u32(&bar_full[s]), kProducerWarps); mbar_init(smem_u32(&bar_empty[s]), 1); }
         mbar_init(smem_u32(&bar_accum), 1);
         mbar_init_fence();
     }
@@ -77,7 +85,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) moe_gemm_kernel(const MoeGemm
                 tok_row[tid] = MODE == 0 ? token : slot;
                 if (MODE == 1) tok_w[tid] = a.pair_w[pair];
             }
-            asm volatile("bar.sync 1, 256;" ::: "memory");
+            asm volatile("bar.sync 1, %0;" ::"n"(kGemmProducers) : "memory");
             if (tid < 128 * MATS) {
                 const int m = tid >> 7, r = tid & 127;
                 // scale rows are a multiple of 8 bytes (K is a multiple of 256)
@@ -97,34 +105,34 @@ __global__ void __launch_bounds__(kGemmThreads, 1) moe_gemm_kernel(const MoeGemm
                 const uint32_t b = max(max(best & 0xff, (best >> 8) & 0xff), max((best >> 16) & 0xff, best >> 24));
                 row_exp[m][r] = any ? (int)b : -1;
             }
-            asm volatile("bar.sync 1, 256;" ::: "memory");
+            asm volatile("bar.sync 1, %0;" ::"n"(kGemmProducers) : "memory");
 
-            // ---- main loop: this thread owns (row, half) of every weight tile and 4 chunks of the token tile
-            const int row = tid >> 1, half = tid & 1;
-            const uint8_t* wsrc[2] = {a.wa_p + e * a.stride_p + (long long)(m0 + row) * (a.K >> 1) + half * 16,
-                                      MODE == 0 ? a.wb_p + e * a.stride_p + (long long)(m0 + row) * (a.K >> 1) + half * 16
-                                                : nullptr};
-            const uint8_t* my_scale[2] = {scale_cache + row * scale_row + half,
-                                          scale_cache + (128 + row) * scale_row + half};
-            const int my_exp[2] = {row_exp[0][row], MODE == 0 ? row_exp[1][row] : 0};
-            const __half* bsrc[4];
-            bool bok[4];
+            // ---- main loop: a thread owns one 32-value block (row, half) of ONE weight tile and 2 chunks of the
+            // token tile (with one weight matrix only half of the producers have a weight block)
+            const int mat = (tid >> 8) & 1;
+            const bool has_a = mat < MATS;
+            const int row = (tid & 255) >> 1, half = tid & 1;
+            const uint8_t* wbase = (mat == 0 || MODE != 0) ? a.wa_p : a.wb_p;
+            const uint8_t* wsrc = wbase + e * a.stride_p + (long long)(m0 + row) * (a.K >> 1) + half * 16;
+            const uint8_t* my_scale = scale_cache + ((has_a ? mat : 0) * 128 + row) * scale_row + half;
+            const int my_exp = row_exp[has_a ? mat : 0][row];
+            const __half* bsrc[2];
+            bool bok[2];
 #pragma unroll
-            for (int q = 0; q < 4; ++q) {
+            for (int q = 0; q < 2; ++q) {
                 const int idx = tid + kGemmProducers * q;
                 const int n = idx >> 3, c = idx & 7;
                 bok[q] = n < n_valid;
                 bsrc[q] = a.act + (size_t)(bok[q] ? tok_row[n] : 0) * a.K + c * 8;
             }
-            uint4 ring_a[4][MATS];
-            uint4 ring_b[2][4];
-            auto load_a = [&](int kb, uint4 (&dst)[MATS]) {
-#pragma unroll
-                for (int m = 0; m < MATS; ++m) dst[m] = ldg_stream_v4(wsrc[m] + (size_t)kb * 32);
+            uint4 ring_a[4];
+            uint4 ring_b[2][2];
+            auto load_a = [&](int kb, uint4& dst) {
+                if (has_a) dst = ldg_stream_v4(wsrc + (size_t)kb * 32);
             };
-            auto load_b = [&](int kb, uint4 (&dst)[4]) {
+            auto load_b = [&](int kb, uint4 (&dst)[2]) {
 #pragma unroll
-                for (int q = 0; q < 4; ++q)
+                for (int q = 0; q < 2; ++q)
                     dst[q] = bok[q] ? __ldcg(reinterpret_cast<const uint4*>(bsrc[q] + (size_t)kb * kGemmKBlock))
                                     : make_uint4(0, 0, 0, 0);
             };
@@ -139,34 +147,42 @@ __global__ void __launch_bounds__(kGemmThreads, 1) moe_gemm_kernel(const MoeGemm
                     if (kb + 3 < n_kb) load_a(kb + 3, ring_a[(u + 3) & 3]);
                     if (kb + 1 < n_kb) load_b(kb + 1, ring_b[(u + 1) & 1]);
                     const uint32_t s = it % S;
+                    long long t0 = clock64();
                     if (it >= (uint32_t)S && alive)
                         alive = mbar_wait_bounded(smem_u32(&bar_empty[s]), ((it / S) - 1) & 1, 4);
+                    long long t1 = clock64();
+                    if (warp == 0) PROF_ADD(MODE * 8 + 0, t1 - t0);
                     uint8_t* stage = gemm_smem + s * L::kStageBytes;
-#pragma unroll
-                    for (int m = 0; m < MATS; ++m) {
-                        const int sb = my_scale[m][kb * 2];
-                        const uint32_t mult = (sb == 255 || my_exp[m] < 0) ? 0u : half_pow2_bits(sb - my_exp[m]);
-                        dequant_block_to_tile(ring_a[u & 3][m], mult, stage + m * kGemmTileBytes, row, half);
+                    if (has_a) {
+                        const int sb = my_scale[kb * 2];
+                        const uint32_t mult = (sb == 255 || my_exp < 0) ? 0u : half_pow2_bits(sb - my_exp);
+                        dequant_block_to_tile(ring_a[u & 3], mult, stage + mat * kGemmTileBytes, row, half);
                     }
 #pragma unroll
-                    for (int q = 0; q < 4; ++q) {
+                    for (int q = 0; q < 2; ++q) {
                         const int idx = tid + kGemmProducers * q;
                         if ((idx >> 3) < n_mma)
                             *reinterpret_cast<uint4*>(stage + MATS * kGemmTileBytes + tc05_sw128_offset(idx >> 3, idx & 7)) =
                                 ring_b[u & 1][q];
                     }
+                    long long t2 = clock64();
                     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                    long long t3 = clock64();
+                    if (warp == 0) { PROF_ADD(MODE * 8 + 6, t2 - t1); PROF_ADD(MODE * 8 + 7, t3 - t2); }
                     __syncwarp();
                     if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(&bar_full[s])) : "memory");
+                    if (warp == 0) { PROF_ADD(MODE * 8 + 1, clock64() - t1); PROF_ADD(MODE * 8 + 2, 1); }
                     ++it;
                 }
             }
         } else {
-            // ---- warp 8: issue the MMAs of every stage; a stage is released when its MMAs have completed
+            // ---- last warp: issue the MMAs of every stage; a stage is released when its MMAs have completed
             const uint32_t idesc = tc05_idesc_f16(128, n_mma);
             for (int kb = 0; kb < n_kb; ++kb, ++it) {
                 const uint32_t s = it % S;
+                long long t0 = clock64();
                 if (alive) alive = mbar_wait_bounded(smem_u32(&bar_full[s]), (it / S) & 1, 5);
+                PROF_ADD(MODE * 8 + 3, clock64() - t0);
                 tc05_fence_after_sync();
                 if (lane == 0 && alive) {
                     const uint32_t stage = smem_u32(gemm_smem) + s * L::kStageBytes;
@@ -187,7 +203,9 @@ __global__ void __launch_bounds__(kGemmThreads, 1) moe_gemm_kernel(const MoeGemm
 
         // ---- epilogue: warps 0..3 own accumulator rows 32 w .. 32 w + 31
         if (warp < 4) {
+            long long t0 = clock64();
             if (alive) alive = mbar_wait_bounded(smem_u32(&bar_accum), tile_count & 1, 6);
+            if (warp == 0) PROF_ADD(MODE * 8 + 4, clock64() - t0);
             tc05_fence_after_sync();
             const int r = tid;                                   // accumulator row = weight row m0 + r
             const uint32_t trow = tmem + ((uint32_t)(warp * 32) << 16);
@@ -217,12 +235,13 @@ __global__ void __launch_bounds__(kGemmThreads, 1) moe_gemm_kernel(const MoeGemm
                 }
             }
         }
+        if (warp == 0) PROF_ADD(MODE * 8 + 5, 1);
         tc05_fence_before_sync();
         __syncthreads();            // accumulators read, token tables free: the next tile may start
         tc05_fence_after_sync();
     }
     __syncthreads();
-    if (warp == 8) tc05_dealloc(tmem, 256);
+    if (warp == kProducerWarps) tc05_dealloc(tmem, 256);
 }
 
 }  // namespace dsv4

@@ -55,8 +55,8 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
 // Returns false (and records `code`) if the phase did not complete within the poll budget.
 __device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity, int code) {
     for (uint32_t it = 0; it < kSpinLimit; ++it) {
-        if (mbar_try_wait(bar, parity)) return true;
-        __nanosleep(32);        // leave the issue slots to the warps that have data
+        if (mbar_try_wait(bar, parity)) return true;   // try_wait itself suspends the thread for a short while
+        if (it > 64) __nanosleep(64);                  // a long wait: leave the issue slots to the other warps
     }
     atomicExch(&g_device_status, code);
     return false;
