@@ -201,6 +201,73 @@ def make_logits(n_steps: int, device, gen, n_experts: int):
     return logits
 
 
+
+def batched_configs(rt, qz, torch, dist, bank, dev, rank, world):
+    """Configurations 3 and 4 (batched decode with Zipf routing, prefill with uniform routing) through the batched
+    tensor-core layer; with several ranks the experts are split contiguously over the ranks and the tokens travel
+    by all-to-all (expert parallel, strong scaling: the token set is fixed).  Rank 0 also checks its tokens against
+    the single-GPU layer on the full bank."""
+    import importlib as _il
+    ep = _il.import_module("dsv4_b200.runtime.expert_parallel")
+    E = bank["w1p"].shape[0]
+    out = {}
+    local_bank = ep.shard_bank(bank, rank, world) if world > 1 else bank
+    for name, T, zipf, seed, iters in (("config3_decode_batch64_zipf", 64, True, 1237, 10),
+                                       ("config4_prefill_4096_uniform", 4096, False, 1238, 5)):
+        g = torch.Generator().manual_seed(seed)                      # identical on every rank
+        if zipf:
+            p = 1.0 / torch.arange(1, E + 1, dtype=torch.float64) ** 1.1
+            ids = torch.multinomial(p.expand(T, E), TOP_K, replacement=False, generator=g)
+        else:
+            ids = torch.rand(T, E, generator=g).topk(TOP_K).indices
+        logit = torch.randn(T, TOP_K, generator=g)
+        w = torch.softmax(logit, -1).float()
+        x = torch.randn(T, HIDDEN, generator=g).to(torch.bfloat16)
+        lo, hi = T * rank // world, T * (rank + 1) // world          # this rank's tokens
+        x_l, ids_l, w_l = x[lo:hi].to(dev), ids[lo:hi].to(torch.int32).to(dev), w[lo:hi].to(dev)
+
+        def local_forward(rows, local_ids, wts):
+            return rt.moe_forward(local_bank, rows, local_ids, wts)
+
+        def step():
+            if world > 1:
+                return ep.ep_moe_forward(x_l, ids_l, w_l, E, local_forward)
+            return rt.moe_forward(bank, x_l, ids_l, w_l)
+
+        y = step()
+        torch.cuda.synchronize()
+        parity = None
+        if world > 1 and rank == 0:
+            ref = rt.moe_forward(bank, x_l, ids_l, w_l).float()
+            parity = float((y.float() - ref).abs().max() / ref.abs().max())
+        for _ in range(2):
+            step()
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(iters):
+            step()
+        b.record()
+        torch.cuda.synchronize()
+        ms = a.elapsed_time(b) / iters
+        if world > 1:
+            t = torch.tensor([ms], device=dev, dtype=torch.float64)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = float(t.item())
+        distinct = int(ids.unique().numel())
+        flops = T * TOP_K * 2 * 3 * HIDDEN * EXPERT_FF
+        min_bytes = distinct * BYTES_PER_EXPERT + 2 * T * HIDDEN * 2
+        out[name] = {"tokens": T, "n_gpus": world, "scaling": "strong", "ms": ms, "tflops": flops / ms / 1e9,
+                     "gbs_min_bytes": min_bytes / ms / 1e6, "distinct_experts": distinct,
+                     "max_abs_vs_1gpu_over_inf_norm": parity,
+                     "exchange": "none" if world == 1 else "torch.distributed all_to_all_single (NCCL): rows out, rows back"}
+    if rt.moe_device_status() != 0:
+        raise RuntimeError("a batched kernel gave up on a bounded wait")
+    return out
+
+
 def run_gpu(args, rank: int, world: int, local_rank: int):
     import torch
     import torch.distributed as dist
@@ -323,6 +390,13 @@ def run_gpu(args, rank: int, world: int, local_rank: int):
 
     if gb.device_status() != 0:
         raise RuntimeError("a kernel gave up on a bounded wait during the benchmark")
+    batched = None
+    if n_experts == N_EXPERTS and not args.no_batched:
+        if world > 1:      # the expert-parallel runs need the same bank on every rank before it is sharded
+            del bank
+            torch.cuda.empty_cache()
+            bank = qz.make_expert_bank(n_experts, HIDDEN, EXPERT_FF, dev, seed=SEED, chunk=16)
+        batched = batched_configs(rt, qz, torch, dist, bank, dev, rank, world)
 
     if world > 1:
         t = torch.tensor([elapsed_ms, e2e_ms, gate_us], device=dev, dtype=torch.float64)
@@ -347,13 +421,16 @@ def run_gpu(args, rank: int, world: int, local_rank: int):
                 "d2h_bytes_per_step": HIDDEN * 2, "steps": e2e_steps,
                 "us_per_layer": e2e_ms / e2e_steps * 1e3,
                 "what": "pinned host x + logits -> device, router, FFN, bf16 out -> pinned host, stream synchronise; every step"},
-        "gpu_launches": 2 * args.steps,
+        "gpu_launches": args.steps,
+        "kernels_per_step": "1 x moe_decode_fused_kernel<4096,2048> (router + gate/up + grid barrier + down)",
         "roofline": {"bound": "hbm", "kernel": "gate_up_ring_kernel<4096> (W1/W3 + SwiGLU, 67 % of the layer's bytes)",
                      "achieved": gate_gbs, "peak": peak, "unit": "GB/s", "frac": gate_gbs / peak,
                      "traffic": GATE_DRAM_TRAFFIC, "algorithmic_bytes": GATE_BYTES, "us_per_launch": gate_us,
                      "peak_source": peak_src},
         "clocks": clocks,
     }
+    if batched is not None:
+        line["batched"] = batched
     if world == 1:
         line["cpu_baseline"] = cpu_baseline(qz)
     print(json.dumps(line), flush=True)
@@ -387,6 +464,7 @@ def main():
     ap.add_argument("--steps", type=int, default=20000)
     ap.add_argument("--warmup", type=int, default=1000)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--no-batched", action="store_true", help="skip the batched / expert-parallel side measurements")
     ap.add_argument("--experts", type=int, default=N_EXPERTS,
                     help="experts in the resident bank; smaller banks (>= 24) are for profiler captures only")
     args = ap.parse_args()
