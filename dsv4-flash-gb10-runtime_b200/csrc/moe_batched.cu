@@ -2,10 +2,13 @@
 // prefill.  No counterpart in the reference (its path is one token at a time,
 // runtime/dsv4_engine_mxfp4.py:412-422 loops tokens); the arithmetic contract is the same FFN:
 //   out[t] = sum_j w[t, j] * W2_e ( silu(W1_e x_t) * (W3_e x_t) ),  e = ids[t, j].
-// Pipeline on the caller's stream: tokens -> normalised fp16; pairs grouped by expert; grouped GEMM 1 (gate/up +
-// SwiGLU) and grouped GEMM 2 (down, router weight applied) on tcgen05 tensor cores (moe_gemm_kernel.cuh);
-// per-token sum in the router's order.  Nothing is allocated; all scratch lives in the caller's workspace.
+// Pipeline on the caller's stream: pairs grouped by expert; grouped GEMM 1 (gate/up + SwiGLU) and grouped GEMM 2
+// (down, router weight applied) on tcgen05 tensor cores; per-token sum in the router's order.  Two tensor-core
+// paths: block-scaled MXFP4 MMAs fed with the packed weights as stored (moe_gemm_mxf4.cuh; activations as three
+// MXFP4 terms; the default), and fp16 MMAs with in-kernel dequantisation (moe_gemm_kernel.cuh; exact operands).
+// Nothing is allocated; all scratch lives in the caller's workspace.
 #include "moe_gemm_kernel.cuh"
+#include "moe_gemm_mxf4.cuh"
 
 #include <cstdio>
 #include <cstdlib>
@@ -20,7 +23,7 @@ struct Carve {
 };
 
 struct WorkspaceMap {
-    size_t xh, xexp, offsets, tiles_up, tiles_down, slot_pair, pair_slot, mid, y, total;
+    size_t xh, xexp, offsets, tiles_up, tiles_down, slot_pair, pair_slot, mid, y, xq, xs, midf, mq, ms, total;
 };
 
 WorkspaceMap map_workspace(long long T, int k, int K, int H, int O, int E) {
@@ -36,6 +39,12 @@ WorkspaceMap map_workspace(long long T, int k, int K, int H, int O, int E) {
     m.pair_slot = c.take((size_t)P * 4);
     m.mid = c.take((size_t)P * H * 2);
     m.y = c.take((size_t)P * O * 4);
+    // block-scaled path: three MXFP4 terms of x and of the FP32 intermediate
+    m.xq = c.take((size_t)3 * T * K / 2);
+    m.xs = c.take((size_t)3 * T * K / 32);
+    m.midf = c.take((size_t)P * H * 4);
+    m.mq = c.take((size_t)3 * P * H / 2);
+    m.ms = c.take((size_t)3 * P * H / 32);
     m.total = c.off;
     return m;
 }
@@ -78,12 +87,13 @@ DSV4_API size_t mxfp4_moe_forward_workspace_bytes(int n_tokens, int k, int K_in,
 // [n_tokens, k] (a token lists an expert at most once), weights FP32 [n_tokens, k]; out bf16 [n_tokens, out_dim].
 // Shapes: K_in and hidden multiples of 256, hidden and out_dim multiples of 128, n_experts <= 1024.
 // Returns 0, -1 bad shape, -2 null / misaligned pointer, -3 launch failure.
-DSV4_API int mxfp4_moe_forward(const __nv_bfloat16* x, const uint8_t* bank_W1_packed, const uint8_t* bank_W3_packed,
+static int moe_forward_impl(int path, const __nv_bfloat16* x, const uint8_t* bank_W1_packed, const uint8_t* bank_W3_packed,
                                const uint8_t* bank_W2_packed, const uint8_t* bank_W1_scale,
                                const uint8_t* bank_W3_scale, const uint8_t* bank_W2_scale, const int* ids,
                                const float* weights, int n_tokens, int n_experts, int K_in, int hidden, int out_dim,
                                int k, __nv_bfloat16* out, void* workspace, cudaStream_t stream) {
     const char* who = "mxfp4_moe_forward";
+    if (path != 0 && path != 1) return -1;
     if (n_tokens < 0 || k <= 0 || n_experts <= 0 || n_experts > kMoeMaxExperts || K_in <= 0 || K_in % 256 != 0 ||
         hidden <= 0 || hidden % 256 != 0 || out_dim <= 0 || out_dim % 128 != 0 || K_in > 16384 || hidden > 16384) {
         std::fprintf(stderr, "%s: unsupported shape T=%d E=%d K=%d H=%d O=%d k=%d\n", who, n_tokens, n_experts, K_in,
@@ -115,10 +125,48 @@ DSV4_API int mxfp4_moe_forward(const __nv_bfloat16* x, const uint8_t* bank_W1_pa
 
     int* status = nullptr;
     cudaGetSymbolAddress(reinterpret_cast<void**>(&status), g_device_status);
-    moe_token_fp16_kernel<<<(n_tokens + 7) / 8, 256, 0, stream>>>(x, n_tokens, K_in, xh, xexp);
     moe_group_kernel<<<1, 1024, 0, stream>>>(ids, P, n_experts, hidden, out_dim, g, status);
-
     const int grid = sm_count();
+
+    if (path == 1) {
+        // ---- block-scaled MXFP4 tensor-core path
+        static int qup_done[64] = {0}, qdown_done[64] = {0};
+        uint8_t* xq = ws + m.xq; uint8_t* xs = ws + m.xs;
+        uint8_t* mq = ws + m.mq; uint8_t* ms = ws + m.ms;
+        float* midf = reinterpret_cast<float*>(ws + m.midf);
+        const int qgrid = 4 * grid;
+        moe_quantize_mxfp4x3_kernel<__nv_bfloat16><<<qgrid, 256, 0, stream>>>(x, n_tokens, K_in, xq, xs);
+        MoeQGemmArgs qu;
+        qu.wa_p = bank_W1_packed; qu.wb_p = bank_W3_packed; qu.wa_s = bank_W1_scale; qu.wb_s = bank_W3_scale;
+        qu.stride_p = (long long)hidden * (K_in / 2); qu.stride_s = (long long)hidden * (K_in / 32);
+        qu.rows = hidden; qu.K = K_in; qu.n_experts = n_experts; qu.k_top = k;
+        qu.act_q = xq; qu.act_s = xs; qu.act_rows = n_tokens; qu.pair_w = weights; qu.g = g; qu.mid = midf; qu.y = nullptr;
+        cudaError_t qerr = allow_smem(moe_gemm_mxf4_kernel<0>, MoeQGemmLayout<0>::kBytes, qup_done);
+        if (qerr == cudaSuccess) {
+            moe_gemm_mxf4_kernel<0><<<grid, kGemmThreads, MoeQGemmLayout<0>::kBytes, stream>>>(qu);
+            moe_quantize_mxfp4x3_kernel<float><<<qgrid, 256, 0, stream>>>(midf, (long long)P, hidden, mq, ms);
+            qerr = cudaGetLastError();
+        }
+        MoeQGemmArgs qd = qu;
+        qd.wa_p = bank_W2_packed; qd.wb_p = nullptr; qd.wa_s = bank_W2_scale; qd.wb_s = nullptr;
+        qd.stride_p = (long long)out_dim * (hidden / 2); qd.stride_s = (long long)out_dim * (hidden / 32);
+        qd.rows = out_dim; qd.K = hidden; qd.act_q = mq; qd.act_s = ms; qd.act_rows = P; qd.mid = nullptr; qd.y = y;
+        if (qerr == cudaSuccess) qerr = allow_smem(moe_gemm_mxf4_kernel<1>, MoeQGemmLayout<1>::kBytes, qdown_done);
+        if (qerr == cudaSuccess) {
+            moe_gemm_mxf4_kernel<1><<<grid, kGemmThreads, MoeQGemmLayout<1>::kBytes, stream>>>(qd);
+            dim3 cgrid((out_dim / 4 + 127) / 128, n_tokens);
+            moe_combine_kernel<<<cgrid, 128, 0, stream>>>(y, g.pair_slot, n_tokens, k, out_dim, out);
+            qerr = cudaGetLastError();
+        }
+        if (qerr != cudaSuccess) {
+            std::fprintf(stderr, "%s: launch failed: %s\n", who, cudaGetErrorString(qerr));
+            return -3;
+        }
+        return 0;
+    }
+
+    // ---- fp16 tensor-core path with in-kernel dequantisation
+    moe_token_fp16_kernel<<<(n_tokens + 7) / 8, 256, 0, stream>>>(x, n_tokens, K_in, xh, xexp);
     MoeGemmArgs up;
     up.wa_p = bank_W1_packed; up.wb_p = bank_W3_packed; up.wa_s = bank_W1_scale; up.wb_s = bank_W3_scale;
     up.stride_p = (long long)hidden * (K_in / 2); up.stride_s = (long long)hidden * (K_in / 32);
@@ -150,6 +198,35 @@ DSV4_API int mxfp4_moe_forward(const __nv_bfloat16* x, const uint8_t* bank_W1_pa
         return -3;
     }
     return 0;
+}
+
+// Default path: block-scaled MXFP4 MMAs; DSV4_B200_MOE_PATH=fp16 in the environment selects the fp16 path.
+DSV4_API int mxfp4_moe_forward(const __nv_bfloat16* x, const uint8_t* bank_W1_packed, const uint8_t* bank_W3_packed,
+                               const uint8_t* bank_W2_packed, const uint8_t* bank_W1_scale,
+                               const uint8_t* bank_W3_scale, const uint8_t* bank_W2_scale, const int* ids,
+                               const float* weights, int n_tokens, int n_experts, int K_in, int hidden, int out_dim,
+                               int k, __nv_bfloat16* out, void* workspace, cudaStream_t stream) {
+    static int path = -1;
+    if (path < 0) {
+        const char* e = std::getenv("DSV4_B200_MOE_PATH");
+        path = (e && e[0] == 'f') ? 0 : 1;
+    }
+    return moe_forward_impl(path, x, bank_W1_packed, bank_W3_packed, bank_W2_packed, bank_W1_scale, bank_W3_scale,
+                            bank_W2_scale, ids, weights, n_tokens, n_experts, K_in, hidden, out_dim, k, out, workspace,
+                            stream);
+}
+
+// The same with the tensor-core path chosen by the caller: 0 = fp16 MMAs with in-kernel dequantisation (operands
+// exact), 1 = block-scaled MXFP4 MMAs (weights as stored, activations as three MXFP4 terms).
+DSV4_API int mxfp4_moe_forward_path(int path, const __nv_bfloat16* x, const uint8_t* bank_W1_packed,
+                                    const uint8_t* bank_W3_packed, const uint8_t* bank_W2_packed,
+                                    const uint8_t* bank_W1_scale, const uint8_t* bank_W3_scale,
+                                    const uint8_t* bank_W2_scale, const int* ids, const float* weights, int n_tokens,
+                                    int n_experts, int K_in, int hidden, int out_dim, int k, __nv_bfloat16* out,
+                                    void* workspace, cudaStream_t stream) {
+    return moe_forward_impl(path, x, bank_W1_packed, bank_W3_packed, bank_W2_packed, bank_W1_scale, bank_W3_scale,
+                            bank_W2_scale, ids, weights, n_tokens, n_experts, K_in, hidden, out_dim, k, out, workspace,
+                            stream);
 }
 
 // 0 unless a kernel of this library gave up on a bounded wait (4 producer, 5 MMA issuer, 6 epilogue) or met an

@@ -117,4 +117,54 @@ __global__ void moe_combine_kernel(const float* __restrict__ y, const int* __res
     *reinterpret_cast<uint2*>(out + (size_t)t * O + o) = packed;
 }
 
+// Rows of activations -> three MXFP4 terms whose sum reproduces the row to ~12 bits:
+//   v ~ q1 * 2^e1 + q2 * 2^e2 + q3 * 2^e3   per 32-element block, q E2M1, 2^e the smallest power of two with
+// amax(what is left) <= 6 * 2^e (no saturation),
+// each term the round-to-nearest E2M1 quantisation of the residual the previous terms left.  The tensor cores
+// multiply FP4 by FP4; three terms are what keeps the layer inside its tolerance (one term: cosine 0.993).
+// Output: q [3][rows][K / 2] packed (low nibble = even element), s [3][rows][K / 32] E8M0 bytes.
+// A lane owns two neighbouring elements, 16 lanes own a block, a warp two blocks.
+template <class Elem>
+__global__ void moe_quantize_mxfp4x3_kernel(const Elem* __restrict__ src, long long rows, int K,
+                                            uint8_t* __restrict__ q, uint8_t* __restrict__ s) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int lane = threadIdx.x & 31;
+    const long long n_pairs = rows * (K / 64);                      // a warp handles 64 consecutive elements
+    const long long term_q = rows * (K / 2), term_s = rows * (K / 32);
+    for (long long w = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); w < n_pairs;
+         w += (long long)gridDim.x * (blockDim.x >> 5)) {
+        const long long e0 = w * 64 + 2 * lane;                     // first of this lane's two elements (row-major)
+        float v0, v1;
+        if constexpr (sizeof(Elem) == 2) {
+            const uint32_t u = *reinterpret_cast<const uint32_t*>(src + e0);
+            v0 = __uint_as_float(u << 16);
+            v1 = __uint_as_float(u & 0xffff0000u);
+        } else {
+            const float2 f = *reinterpret_cast<const float2*>(src + e0);
+            v0 = f.x; v1 = f.y;
+        }
+#pragma unroll
+        for (int t = 0; t < 3; ++t) {
+            uint32_t m = max(__float_as_uint(v0) & 0x7fffffffu, __float_as_uint(v1) & 0x7fffffffu);
+#pragma unroll
+            for (int off = 8; off > 0; off >>= 1) m = max(m, __shfl_xor_sync(kFullMask, m, off));   // 16-lane block
+            int e = (int)(m >> 23) - 127 - 2;                       // amax / 2^e in [4, 8)
+            if ((m & 0x007fffffu) > 0x00400000u) e += 1;             // above 6 * 2^e the E2M1 grid would saturate
+            e = min(max(e, -127), 127);
+            if (m == 0) e = -127;
+            const float inv = __uint_as_float((uint32_t)min(max(127 - e, 1), 254) << 23);
+            const float sc = __uint_as_float((uint32_t)max(e + 127, 1) << 23);                     // 2^e (>= 2^-126)
+            uint16_t packed;
+            asm("{\n .reg .b8 b;\n cvt.rn.satfinite.e2m1x2.f32 b, %2, %1;\n mov.b16 %0, {b, 0};\n}"
+                : "=h"(packed) : "f"(v0 * inv), "f"(v1 * inv));
+            const float2 back = e2m1x2_to_float2(packed);
+            v0 -= back.x * sc;
+            v1 -= back.y * sc;
+            q[t * term_q + (e0 >> 1)] = (uint8_t)packed;
+            if ((lane & 15) == 0) s[t * term_s + (e0 >> 5)] = (uint8_t)(e + 127);
+        }
+    }
+}
+
 }  // namespace dsv4

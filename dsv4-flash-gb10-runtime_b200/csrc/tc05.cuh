@@ -82,4 +82,57 @@ __device__ __forceinline__ uint32_t tc05_sw128_offset(int row, int chunk) {
     return (uint32_t)row * 128u + (uint32_t)((chunk ^ (row & 7)) << 4);
 }
 
+// ---------------------------------------------------------------------------------------------------------------
+// Block-scaled MMA (kind::mxf4: E2M1 operands, one UE8M0 scale per 32 K-elements, scales in tensor memory)
+// ---------------------------------------------------------------------------------------------------------------
+// Operand tiles are K-major, 128-byte swizzled like the fp16 ones; a 128-byte row now holds 256 E2M1 values and one
+// MMA consumes 64 of them (32 bytes), so K-step j still adds 32 j bytes to the descriptor's start address.
+//
+// Scale factors of a 128-row x 128-K-element piece (4 scale bytes per row) form a 512-byte "atom" in shared
+// memory: byte (row r, scale j) at (r % 32) * 16 + (r / 32) * 4 + j.  tcgen05.cp (32x128b, warpx4) copies an atom
+// into 4 tensor-memory columns (lane = r % 32 replicated in the four lane quadrants, column = r / 32, byte = j);
+// an MMA with K = 64 uses two of the four bytes, selected by the scale-factor id field of the instruction
+// descriptor (0: bytes 0-1, 2: bytes 2-3).
+
+// Instruction descriptor of kind::mxf4 block-scaled: B scale id at bit 4, A / B formats 1 (E2M1) at bits 7 / 10,
+// N >> 3 at bit 17, scale format 1 (UE8M0) at bit 23, M >> 4 at bit 24, A scale id at bit 29.
+__device__ __forceinline__ uint32_t tc05_idesc_mxf4(int m, int n, int a_sf_id, int b_sf_id) {
+    return ((uint32_t)b_sf_id << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | (1u << 23) |
+           ((uint32_t)(m >> 4) << 24) | ((uint32_t)a_sf_id << 29);
+}
+
+// Shared-memory descriptor of one scale atom: 32 rows x 16 bytes, no swizzle, 8-row groups 128 bytes apart.
+__device__ __forceinline__ uint64_t tc05_desc_scale_atom(uint32_t smem_addr) {
+    uint64_t d = 0;
+    d |= (uint64_t)((smem_addr >> 4) & 0x3fff);
+    d |= (uint64_t)(128 >> 4) << 32;
+    d |= (uint64_t)1 << 46;
+    return d;
+}
+
+// Scale atom: shared memory -> 4 tensor-memory columns starting at `tmem_col`.  Issued by ONE thread; ordered with
+// the MMAs that thread issues afterwards.
+__device__ __forceinline__ void tc05_copy_scale_atom(uint32_t tmem_col, uint32_t smem_atom_addr) {
+    asm volatile("tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], %1;" ::"r"(tmem_col),
+                 "l"(tc05_desc_scale_atom(smem_atom_addr))
+                 : "memory");
+}
+
+__device__ __forceinline__ void tc05_mma_mxf4(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc,
+                                              uint32_t tmem_sfa, uint32_t tmem_sfb, uint32_t accumulate) {
+    asm volatile(
+        "{\n"
+        " .reg .pred p;\n"
+        " setp.ne.b32 p, %6, 0;\n"
+        " tcgen05.mma.cta_group::1.kind::mxf4.block_scale.scale_vec::2X [%0], %1, %2, %3, [%4], [%5], p;\n"
+        "}\n" ::"r"(tmem_d),
+        "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(tmem_sfa), "r"(tmem_sfb), "r"(accumulate)
+        : "memory");
+}
+
+// Byte offset of scale (row r, scale j of 4) inside a scale atom.
+__device__ __forceinline__ uint32_t tc05_scale_atom_offset(int r, int j) {
+    return (uint32_t)((r & 31) * 16 + (r >> 5) * 4 + j);
+}
+
 }  // namespace dsv4

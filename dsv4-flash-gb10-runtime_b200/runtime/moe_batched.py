@@ -22,7 +22,11 @@ def forward_workspace_bytes(n_tokens: int, k: int, K_in: int, hidden: int, out_d
 
 
 def moe_forward(bank: Dict[str, torch.Tensor], x: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor,
-                out: Optional[torch.Tensor] = None, workspace: Optional[torch.Tensor] = None) -> torch.Tensor:
+                out: Optional[torch.Tensor] = None, workspace: Optional[torch.Tensor] = None,
+                path: Optional[str] = None) -> torch.Tensor:
+    """`path`: None = the library's default (block-scaled MXFP4 MMAs unless DSV4_B200_MOE_PATH=fp16), 'mxf4' =
+    block-scaled MMAs fed with the packed weights (activations as three MXFP4 terms), 'fp16' = fp16 MMAs with
+    in-kernel dequantisation (exact operands)."""
     lib = _capi.load("moe")
     for name, t, dt in (("x", x, torch.bfloat16), ("ids", ids, torch.int32), ("weights", weights, torch.float32)):
         if not t.is_cuda or t.dtype != dt or not t.is_contiguous():
@@ -38,10 +42,14 @@ def moe_forward(bank: Dict[str, torch.Tensor], x: torch.Tensor, ids: torch.Tenso
         out = torch.empty(T, out_dim, dtype=torch.bfloat16, device=x.device)
     if workspace is None:
         workspace = torch.empty(forward_workspace_bytes(T, k, K, hidden, out_dim, E), dtype=torch.uint8, device=x.device)
-    rc = lib.mxfp4_moe_forward(_capi.ptr(x), _capi.ptr(bank["w1p"]), _capi.ptr(bank["w3p"]), _capi.ptr(bank["w2p"]),
+    args = (_capi.ptr(x), _capi.ptr(bank["w1p"]), _capi.ptr(bank["w3p"]), _capi.ptr(bank["w2p"]),
                                _capi.ptr(bank["w1s"]), _capi.ptr(bank["w3s"]), _capi.ptr(bank["w2s"]), _capi.ptr(ids),
                                _capi.ptr(weights), c_int(T), c_int(E), c_int(K), c_int(hidden), c_int(out_dim), c_int(k),
                                _capi.ptr(out), _capi.ptr(workspace), _capi.stream_ptr(x.device))
+    if path is None:
+        rc = lib.mxfp4_moe_forward(*args)
+    else:
+        rc = lib.mxfp4_moe_forward_path(c_int({"fp16": 0, "mxf4": 1}[path]), *args)
     if rc != 0:
         raise RuntimeError(f"mxfp4_moe_forward returned {rc}")
     return out

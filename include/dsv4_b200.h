@@ -133,6 +133,14 @@ int mxfp4_moe_forward(const uint16_t* x, const uint8_t* bank_W1_packed, const ui
                       const uint8_t* bank_W2_packed, const uint8_t* bank_W1_scale, const uint8_t* bank_W3_scale,
                       const uint8_t* bank_W2_scale, const int* ids, const float* weights, int n_tokens, int n_experts,
                       int K_in, int hidden, int out_dim, int k, uint16_t* out, void* workspace, void* stream);
+/* The same with the tensor-core path chosen by the caller: 1 = block-scaled MXFP4 MMAs fed with the packed weights as
+ * stored, activations as three MXFP4 terms (what mxfp4_moe_forward uses unless DSV4_B200_MOE_PATH=fp16 is set);
+ * 0 = fp16 MMAs with in-kernel dequantisation (exact operands). */
+int mxfp4_moe_forward_path(int path, const uint16_t* x, const uint8_t* bank_W1_packed, const uint8_t* bank_W3_packed,
+                           const uint8_t* bank_W2_packed, const uint8_t* bank_W1_scale, const uint8_t* bank_W3_scale,
+                           const uint8_t* bank_W2_scale, const int* ids, const float* weights, int n_tokens,
+                           int n_experts, int K_in, int hidden, int out_dim, int k, uint16_t* out, void* workspace,
+                           void* stream);
 size_t mxfp4_moe_forward_workspace_bytes(int n_tokens, int k, int K_in, int hidden, int out_dim, int n_experts);
 /* 0, or the code a kernel of this library recorded since the last call (3 bad expert id, 4/5/6 a bounded wait ran
  * out); clears it.  Synchronises the device. */

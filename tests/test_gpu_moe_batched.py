@@ -19,13 +19,14 @@ def routing(T, E, k, seed, zipf=False):
     return ids.to(torch.int32), w.float()
 
 
+@pytest.mark.parametrize("path", ["mxf4", "fp16"])
 @pytest.mark.parametrize("T,E,K,H,O,k,zipf", [
     (1, 4, 256, 256, 128, 2, False),          # a single token
     (20, 8, 256, 256, 256, 2, False),
     (64, 16, 512, 512, 384, 6, True),         # skewed: some experts get most tokens, some none
     (300, 3, 256, 512, 256, 2, False),        # more than 128 tokens per expert: several token tiles
 ])
-def test_moe_forward_small(rt, qz, T, E, K, H, O, k, zipf):
+def test_moe_forward_small(rt, qz, T, E, K, H, O, k, zipf, path):
     dev = torch.device("cuda:0")
     bank = qz.make_expert_bank(E, K, H, "cpu", seed=T + E)
     if O != K:                                  # down projection to a different width
@@ -34,27 +35,31 @@ def test_moe_forward_small(rt, qz, T, E, K, H, O, k, zipf):
         bank["w2p"], bank["w2s"] = qz.quantize_mxfp4(w2)
     x = (torch.randn(T, K, generator=torch.Generator().manual_seed(1)) * 3.0).to(torch.bfloat16)
     ids, w = routing(T, E, k, seed=5, zipf=zipf)
-    out = rt.moe_forward({n: v.to(dev) for n, v in bank.items()}, x.to(dev), ids.to(dev), w.to(dev))
+    out = rt.moe_forward({n: v.to(dev) for n, v in bank.items()}, x.to(dev), ids.to(dev), w.to(dev), path=path)
     torch.cuda.synchronize()
     assert rt.moe_device_status() == 0
     ref = oracle.moe_layer_ref(x, bank, ids.numpy(), w.numpy())
     got = out.float().cpu().numpy()
     err, cos = oracle.max_abs_rel(got, ref), oracle.cosine(got, ref)
     assert err <= 1e-2 and cos >= 0.9999, f"max-abs/inf {err:.3e} cosine {cos:.7f}"
-    assert err <= 5e-3 and cos >= 0.99999, f"(tight) max-abs/inf {err:.3e} cosine {cos:.7f}"
+    # the fp16 path has exact operands; the block-scaled path carries the 3-term MXFP4 error of the activations
+    tight = (5e-3, 0.99999) if path == "fp16" else (7e-3, 0.99997)
+    assert err <= tight[0] and cos >= tight[1], f"(tight) max-abs/inf {err:.3e} cosine {cos:.7f}"
+    print(f"{path}: max-abs/inf {err:.3e} cosine {cos:.7f}")
     # deterministic
-    again = rt.moe_forward({n: v.to(dev) for n, v in bank.items()}, x.to(dev), ids.to(dev), w.to(dev))
+    again = rt.moe_forward({n: v.to(dev) for n, v in bank.items()}, x.to(dev), ids.to(dev), w.to(dev), path=path)
     assert torch.equal(out.view(torch.int16), again.view(torch.int16))
 
 
-def test_moe_forward_matches_single_token_path(rt, qz):
+@pytest.mark.parametrize("path", ["mxf4", "fp16"])
+def test_moe_forward_matches_single_token_path(rt, qz, path):
     """Batched decode at the DSv4 expert shape against the one-token decode kernel, token by token."""
     dev = torch.device("cuda:0")
     T, E, K, H, k = 8, 12, 4096, 2048, 6
     bank = {n: v for n, v in qz.make_expert_bank(E, K, H, dev, seed=3).items()}
     x = torch.randn(T, K, generator=torch.Generator().manual_seed(2)).to(torch.bfloat16).to(dev)
     ids, w = routing(T, E, k, seed=8)
-    out = rt.moe_forward(bank, x, ids.to(dev), w.to(dev))
+    out = rt.moe_forward(bank, x, ids.to(dev), w.to(dev), path=path)
     for t in range(T):
         one = rt.mxfp4_grouped_gemv_ids(bank, ids[t].contiguous().to(dev), x[t].contiguous(), w[t].contiguous().to(dev))
         d = (out[t].float() - one.float()).abs().max() / one.float().abs().max()
@@ -62,7 +67,8 @@ def test_moe_forward_matches_single_token_path(rt, qz):
     assert rt.moe_device_status() == 0
 
 
-def test_moe_forward_scale_invariance(rt, qz):
+@pytest.mark.parametrize("path", ["mxf4", "fp16"])
+def test_moe_forward_scale_invariance(rt, qz, path):
     """x scaled by 2^20 and 2^-20: the normalisation must keep fp16 operands in range; the output follows x
     through the SwiGLU (checked against the oracle on the scaled input)."""
     dev = torch.device("cuda:0")
@@ -71,7 +77,7 @@ def test_moe_forward_scale_invariance(rt, qz):
     ids, w = routing(T, E, k, seed=3)
     for scale in (2.0 ** 20, 2.0 ** -20):
         x = (torch.randn(T, K, generator=torch.Generator().manual_seed(4)) * scale).to(torch.bfloat16)
-        out = rt.moe_forward({n: v.to(dev) for n, v in bank.items()}, x.to(dev), ids.to(dev), w.to(dev))
+        out = rt.moe_forward({n: v.to(dev) for n, v in bank.items()}, x.to(dev), ids.to(dev), w.to(dev), path=path)
         ref = oracle.moe_layer_ref(x, bank, ids.numpy(), w.numpy())
         got = out.float().cpu().numpy()
         assert np.isfinite(got).all()
