@@ -125,7 +125,8 @@ static int moe_forward_impl(int path, const __nv_bfloat16* x, const uint8_t* ban
 
     int* status = nullptr;
     cudaGetSymbolAddress(reinterpret_cast<void**>(&status), g_device_status);
-    moe_group_kernel<<<1, 1024, 0, stream>>>(ids, P, n_experts, hidden, out_dim, g, status);
+    moe_group_kernel<<<1, 1024, 0, stream>>>(ids, P, n_experts, hidden, out_dim, path == 1 ? kQTokUp : kMoeTileTokens,
+                                             path == 1 ? kQTokDown : kMoeTileTokens, g, status);
     const int grid = sm_count();
 
     if (path == 1) {
@@ -237,10 +238,3 @@ DSV4_API int mxfp4_moe_device_status(void) {
     if (v != 0) cudaMemcpyToSymbol(g_device_status, &zero, sizeof(int));
     return v;
 }
-
-#ifdef DSV4_EXP_PROF
-DSV4_API void mxfp4_moe_prof(long long* out64, int reset) {
-    cudaMemcpyFromSymbol(out64, g_prof, sizeof(long long) * 64);
-    if (reset) { long long z[64] = {0}; cudaMemcpyToSymbol(g_prof, z, sizeof(z)); }
-}
-#endif

@@ -5,13 +5,6 @@
 
 namespace dsv4 {
 
-#ifdef DSV4_EXP_PROF
-__device__ long long g_prof[64];
-#define PROF_ADD(i, v) do { if (blockIdx.x == 0 && lane == 0) atomicAdd((unsigned long long*)&g_prof[(i)], (unsigned long long)(v)); } while (0)
-#else
-#define PROF_ADD(i, v) do { } while (0)
-#endif
-
 template <int MODE>
 __global__ void __launch_bounds__(kGemmThreads, 1) moe_gemm_kernel(const MoeGemmArgs a) {
     using L = MoeGemmLayout<MODE>;
@@ -147,11 +140,8 @@ __global__ void __launch_bounds__(kGemmThreads, 1) moe_gemm_kernel(const MoeGemm
                     if (kb + 3 < n_kb) load_a(kb + 3, ring_a[(u + 3) & 3]);
                     if (kb + 1 < n_kb) load_b(kb + 1, ring_b[(u + 1) & 1]);
                     const uint32_t s = it % S;
-                    long long t0 = clock64();
                     if (it >= (uint32_t)S && alive)
                         alive = mbar_wait_bounded(smem_u32(&bar_empty[s]), ((it / S) - 1) & 1, 4);
-                    long long t1 = clock64();
-                    if (warp == 0) PROF_ADD(MODE * 8 + 0, t1 - t0);
                     uint8_t* stage = gemm_smem + s * L::kStageBytes;
                     if (has_a) {
                         const int sb = my_scale[kb * 2];
@@ -165,13 +155,9 @@ __global__ void __launch_bounds__(kGemmThreads, 1) moe_gemm_kernel(const MoeGemm
                             *reinterpret_cast<uint4*>(stage + MATS * kGemmTileBytes + tc05_sw128_offset(idx >> 3, idx & 7)) =
                                 ring_b[u & 1][q];
                     }
-                    long long t2 = clock64();
                     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-                    long long t3 = clock64();
-                    if (warp == 0) { PROF_ADD(MODE * 8 + 6, t2 - t1); PROF_ADD(MODE * 8 + 7, t3 - t2); }
                     __syncwarp();
                     if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(&bar_full[s])) : "memory");
-                    if (warp == 0) { PROF_ADD(MODE * 8 + 1, clock64() - t1); PROF_ADD(MODE * 8 + 2, 1); }
                     ++it;
                 }
             }
@@ -180,9 +166,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) moe_gemm_kernel(const MoeGemm
             const uint32_t idesc = tc05_idesc_f16(128, n_mma);
             for (int kb = 0; kb < n_kb; ++kb, ++it) {
                 const uint32_t s = it % S;
-                long long t0 = clock64();
                 if (alive) alive = mbar_wait_bounded(smem_u32(&bar_full[s]), (it / S) & 1, 5);
-                PROF_ADD(MODE * 8 + 3, clock64() - t0);
                 tc05_fence_after_sync();
                 if (lane == 0 && alive) {
                     const uint32_t stage = smem_u32(gemm_smem) + s * L::kStageBytes;
@@ -203,9 +187,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) moe_gemm_kernel(const MoeGemm
 
         // ---- epilogue: warps 0..3 own accumulator rows 32 w .. 32 w + 31
         if (warp < 4) {
-            long long t0 = clock64();
             if (alive) alive = mbar_wait_bounded(smem_u32(&bar_accum), tile_count & 1, 6);
-            if (warp == 0) PROF_ADD(MODE * 8 + 4, clock64() - t0);
             tc05_fence_after_sync();
             const int r = tid;                                   // accumulator row = weight row m0 + r
             const uint32_t trow = tmem + ((uint32_t)(warp * 32) << 16);
@@ -235,7 +217,6 @@ __global__ void __launch_bounds__(kGemmThreads, 1) moe_gemm_kernel(const MoeGemm
                 }
             }
         }
-        if (warp == 0) PROF_ADD(MODE * 8 + 5, 1);
         tc05_fence_before_sync();
         __syncthreads();            // accumulators read, token tables free: the next tile may start
         tc05_fence_after_sync();

@@ -3,15 +3,21 @@
 // (packed nibbles + E8M0 bytes) - no dequantisation instruction is executed, and a weight costs half a byte of
 // shared-memory traffic instead of the four bytes the fp16 path (moe_gemm_kernel.cuh) pays.
 //
-// The tensor cores multiply FP4 by FP4, so the activations are given as three MXFP4 terms (moe_prep.cuh) and every
-// weight tile is multiplied by each of them, accumulating into the same FP32 accumulator:
+// The tensor cores multiply FP4 by FP4, so the activations are given as three MXFP4 terms (moe_prep.cuh):
 //   D = W * (q1 + q2 + q3) = W q1 + W q2 + W q3.
+// On B200 one tcgen05.mma of M = 128 occupies the tensor pipe for about the same ~190 clocks whether N is 32 or
+// 256 (measured), so the MMA count, not the flop count, decides the speed of this kernel.  The three terms are
+// therefore STACKED ALONG N: the B operand of a tile holds term 1 of its tokens in rows [0, n), term 2 in [n, 2n),
+// term 3 in [2n, 3n), and one MMA of N = 3n produces the three partial products in three column ranges of the
+// accumulator, which the epilogue adds.  When 3n > 256 (the MMA's largest N) the third term moves to row 256 and
+// gets an MMA of its own.
 //
-// Tiles: 128 weight rows (M) x up to 128 tokens (N); a stage covers 256 K-elements (one 128-byte swizzled row per
-// operand row = 4 MMAs of K = 64).  Per stage the 16 producer warps copy: the packed weight rows (one or two
-// matrices), the three packed activation terms of the tile's tokens, and the scale bytes re-arranged into
-// 512-byte scale atoms; one lane of the last warp copies the atoms into tensor memory (tcgen05.cp) and issues the
-// MMAs; tcgen05.commit releases the stage.  Persistent grid, one CTA per SM.  Every wait is bounded.
+// Tiles: 128 weight rows (M) of one matrix (down) or of W1 and W3 (gate/up, two accumulators) x up to kTok
+// tokens; a stage covers 256 K-elements (one 128-byte swizzled row per operand row = 4 MMAs of K = 64).  Per stage
+// the 16 producer warps copy with cp.async: the packed weight rows, the three packed activation terms of the
+// tile's tokens, and the scale bytes re-arranged into 512-byte scale atoms; one lane of the last warp copies the
+// atoms into tensor memory (tcgen05.cp) and issues the MMAs; tcgen05.commit releases the stage.  Persistent grid,
+// one CTA per SM.  Every wait is bounded.
 #pragma once
 
 #include "moe_gemm.cuh"
@@ -20,8 +26,9 @@ namespace dsv4 {
 
 constexpr int kQKBlock = 256;                        // K-elements per stage
 constexpr int kQTerms = 3;                           // activation terms
-constexpr uint32_t kQTile = 128 * 128;               // bytes of one packed operand tile (128 rows x 128 B)
-constexpr uint32_t kQAtoms = 2 * 512;                // scale bytes of one operand per stage (2 atoms)
+constexpr uint32_t kQTile = 128 * 128;               // bytes of one packed weight tile (128 rows x 128 B)
+constexpr int kQTokUp = 64;                          // tokens per gate/up tile (3 x 64 = 192 accumulator columns x 2)
+constexpr int kQTokDown = 128;                       // tokens per down tile
 
 struct MoeQGemmArgs {
     const uint8_t* wa_p; const uint8_t* wb_p;        // up: W1, W3 packed; down: W2
@@ -40,17 +47,25 @@ struct MoeQGemmArgs {
 template <int MODE>
 struct MoeQGemmLayout {
     static constexpr int kMats = MODE == 0 ? 2 : 1;
-    static constexpr int kStages = MODE == 0 ? 2 : 3;
+    static constexpr int kTok = MODE == 0 ? kQTokUp : kQTokDown;
+    static constexpr int kStages = 3;
+    // rows of the stacked B operand: contiguous when the three terms fit one MMA, else term 3 at row 256
+    static constexpr int kBRows = 3 * kTok <= 256 ? 3 * kTok : 256 + kTok;
+    static constexpr int kRowGroups = (kBRows + 127) / 128;                  // scale atoms cover 128 rows
     static constexpr uint32_t kOffB = kMats * kQTile;
-    static constexpr uint32_t kOffSfA = kOffB + kQTerms * kQTile;
-    static constexpr uint32_t kOffSfB = kOffSfA + kMats * kQAtoms;
-    static constexpr uint32_t kStageBytes = kOffSfB + kQTerms * kQAtoms;     // 87 040 (up) / 69 632 (down)
+    static constexpr uint32_t kOffSfA = kOffB + kBRows * 128;
+    static constexpr uint32_t kOffSfB = kOffSfA + kMats * 1024;              // [mat][k-atom] x 512 B
+    static constexpr uint32_t kStageBytes = kOffSfB + 2 * kRowGroups * 512;  // [k-atom][row group] x 512 B
     static constexpr uint32_t kBytes = kStages * kStageBytes + 1024;
-    // tensor memory: accumulators first, then per stage the scale columns of every operand (8 columns each)
-    static constexpr uint32_t kAccCols = kMats * 128;
-    static constexpr uint32_t kSfColsPerStage = (kMats + kQTerms) * 8;
+    // tensor memory: accumulators (one column per B row) first, then per stage the scale columns
+    static constexpr uint32_t kAccStride = kBRows;
+    static constexpr uint32_t kAccCols = kMats * kAccStride;
+    static constexpr uint32_t kSfBCol = kMats * 8;                           // B scales after the A scales
+    static constexpr uint32_t kSfColsPerStage = kMats * 8 + 2 * kRowGroups * 4;
     static_assert(kStageBytes % 1024 == 0, "stage size must keep tiles 1024-byte aligned");
     static_assert(kAccCols + kStages * kSfColsPerStage <= 512, "tensor memory overflow");
+    static_assert(kMats * 128 + kQTerms * kTok <= kGemmProducers, "one scale row per producer thread");
+    static_assert(kBytes <= 227 * 1024, "shared memory overflow");
 };
 
 template <int MODE>
@@ -58,12 +73,15 @@ __global__ void __launch_bounds__(kGemmThreads, 1) moe_gemm_mxf4_kernel(const Mo
     using L = MoeQGemmLayout<MODE>;
     constexpr int S = L::kStages;
     constexpr int MATS = L::kMats;
+    constexpr int TOK = L::kTok;
+    constexpr int RG = L::kRowGroups;
     constexpr int kProducerWarps = kGemmProducers / 32;
+    constexpr int kBChunks = (TOK * 8 + kGemmProducers - 1) / kGemmProducers;   // 16-byte chunks per thread and term
     extern __shared__ __align__(1024) uint8_t gemm_smem[];
     __shared__ __align__(8) uint64_t bar_full[S], bar_empty[S], bar_accum;
     __shared__ uint32_t tmem_holder;
-    __shared__ int tok_row[128];             // activation row of every accumulator column
-    __shared__ float tok_w[128];             // router weight of every column (down)
+    __shared__ int tok_row[128];             // activation row of every token of the tile
+    __shared__ float tok_w[128];             // router weight of every token (down)
     pdl_launch_dependents();
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -73,7 +91,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) moe_gemm_mxf4_kernel(const Mo
 
     if (warp == kProducerWarps) tc05_alloc(smem_u32(&tmem_holder), 512);
     if (tid == 0) {
-        for (int s = 0; s < S; ++s) { mbar_init(smem_u32(&bar_full[s]), kProducerWarps); mbar_init(smem_u32(&bar_empty[s]), 1); }
+        for (int s = 0; s < S; ++s) { mbar_init(smem_u32(&bar_full[s]), kGemmProducers); mbar_init(smem_u32(&bar_empty[s]), 1); }
         mbar_init(smem_u32(&bar_accum), 1);
         mbar_init_fence();
     }
@@ -98,10 +116,13 @@ __global__ void __launch_bounds__(kGemmThreads, 1) moe_gemm_mxf4_kernel(const Mo
         const int e = lo;
         const int local = tile - tiles[e];
         const int nt = local / m_tiles, mt = local - nt * m_tiles;
-        const int slot0 = a.g.offsets[e] + nt * kMoeTileTokens;
-        const int n_valid = min(kMoeTileTokens, a.g.offsets[e + 1] - slot0);
+        const int slot0 = a.g.offsets[e] + nt * TOK;
+        const int n_valid = min(TOK, a.g.offsets[e + 1] - slot0);
         const int n_mma = (n_valid + 15) & ~15;
         const int m0 = mt * kMoeTileRows;
+        // B rows (= accumulator columns) of the three terms
+        const bool split = 3 * n_mma > 256;
+        const int term_row2 = split ? 256 : 2 * n_mma;
 
         if (producer) {
             if (tid < n_valid) {
@@ -114,118 +135,120 @@ __global__ void __launch_bounds__(kGemmThreads, 1) moe_gemm_mxf4_kernel(const Mo
 
             // what this thread copies in every stage
             // weights: chunk (row, c) of each matrix; 128 rows x 8 chunks = 1024 per matrix, 2 per thread
-            // activations: chunk (n, c) of each term; scales: one row of 8 bytes per 128 threads and operand
             const int wr[2] = {tid >> 3, (tid + kGemmProducers) >> 3};
             const int wc = tid & 7;
-            const uint8_t* wsrc[2][2];
+            const uint8_t* wsrc[MATS][2];
 #pragma unroll
             for (int m = 0; m < MATS; ++m)
 #pragma unroll
                 for (int h = 0; h < 2; ++h)
                     wsrc[m][h] = (m == 0 ? a.wa_p : a.wb_p) + e * a.stride_p + (long long)(m0 + wr[h]) * row_p + wc * 16;
-            const uint8_t* bsrc[2];
-            bool bok[2], bwrite[2];
+            // activations: chunk (token, c) of each term
+            const uint8_t* bsrc[kBChunks];
+            bool bok[kBChunks], bwrite[kBChunks];
 #pragma unroll
-            for (int h = 0; h < 2; ++h) {
+            for (int h = 0; h < kBChunks; ++h) {
                 bok[h] = wr[h] < n_valid;
                 bwrite[h] = wr[h] < n_mma;
                 bsrc[h] = a.act_q + (long long)(bok[h] ? tok_row[wr[h]] : 0) * row_p + wc * 16;
             }
-            // scale rows: threads 0..127 matrix A rows, 128..255 matrix B rows (up), then 3 x 128 for the terms
-            const int sf_op = tid >> 7, sf_row = tid & 127;               // operand index 0 .. 3 (4 x 128 threads)
-            const uint8_t* sfsrc[2] = {nullptr, nullptr};                  // up to two operands per thread
-            uint32_t sfdst[2] = {0, 0};
-            bool sfok[2] = {false, false};
-#pragma unroll
-            for (int h = 0; h < 2; ++h) {
-                const int op = sf_op + 4 * h;                              // 0 .. MATS-1 weights, then the terms
-                if (op < MATS) {
-                    sfsrc[h] = (op == 0 ? a.wa_s : a.wb_s) + e * a.stride_s + (long long)(m0 + sf_row) * row_s;
-                    sfdst[h] = L::kOffSfA + op * kQAtoms;
-                    sfok[h] = true;
-                } else if (op < MATS + kQTerms) {
-                    const int t = op - MATS;
-                    sfok[h] = true;
-                    sfdst[h] = L::kOffSfB + t * kQAtoms;
-                    sfsrc[h] = sf_row < n_valid
-                                   ? a.act_s + (long long)t * a.act_rows * row_s + (long long)tok_row[sf_row] * row_s
-                                   : nullptr;                              // padding columns: scale 1, data 0
+            // scales: one row of 8 bytes per thread; threads [0, 128 MATS) the weight rows, then TOK per term
+            const uint8_t* sfsrc = nullptr;
+            uint32_t sfdst = 0;
+            bool sfok = false;
+            if (tid < MATS * 128) {
+                const int m = tid >> 7, r = tid & 127;
+                sfsrc = (m == 0 ? a.wa_s : a.wb_s) + e * a.stride_s + (long long)(m0 + r) * row_s;
+                sfdst = L::kOffSfA + m * 1024 + tc05_scale_atom_offset(r, 0);
+                sfok = true;
+            } else if (tid < MATS * 128 + kQTerms * TOK) {
+                const int idx = tid - MATS * 128;
+                const int t = idx / TOK, n = idx - t * TOK;
+                if (n < n_mma) {
+                    const int brow = (t == 2 ? term_row2 : t * n_mma) + n;
+                    sfok = true;
+                    sfdst = L::kOffSfB + (brow >> 7) * 512 + tc05_scale_atom_offset(brow & 127, 0);
+                    if (n < n_valid)                                  // padding rows: scale 1, data 0
+                        sfsrc = a.act_s + (long long)t * a.act_rows * row_s + (long long)tok_row[n] * row_s;
                 }
             }
+            const uint32_t sf_atom_stride = tid < MATS * 128 ? 512u : (uint32_t)RG * 512u;   // k-atom 0 -> 1
 
+            // Weights and activation terms go global -> shared memory with asynchronous 16-byte copies (no
+            // registers in between).  Every producer thread makes the stage's "full" barrier arrive when ITS copies
+            // have landed (cp.async.mbarrier.arrive), so a stage is published the moment its last byte arrives
+            // while the thread is already filling the next free stage.
             for (int kb = 0; kb < n_kb; ++kb, ++it) {
-                // ---- requests first (they are what takes long), stores after the stage is free
-                uint4 wv[MATS][2], bv[kQTerms][2];
-                uint2 sv[2];
-#pragma unroll
-                for (int m = 0; m < MATS; ++m)
-#pragma unroll
-                    for (int h = 0; h < 2; ++h) wv[m][h] = ldg_stream_v4(wsrc[m][h] + (size_t)kb * 128);
-#pragma unroll
-                for (int t = 0; t < kQTerms; ++t)
-#pragma unroll
-                    for (int h = 0; h < 2; ++h)
-                        bv[t][h] = bok[h] ? __ldcg(reinterpret_cast<const uint4*>(bsrc[h] + (long long)t * a.act_rows * row_p +
-                                                                                    (size_t)kb * 128))
-                                          : make_uint4(0, 0, 0, 0);
-#pragma unroll
-                for (int h = 0; h < 2; ++h) {
-                    sv[h] = make_uint2(0x7f7f7f7fu, 0x7f7f7f7fu);
-                    if (sfok[h] && sfsrc[h]) sv[h] = __ldcg(reinterpret_cast<const uint2*>(sfsrc[h] + (size_t)kb * 8));
-                }
+                uint2 sv = make_uint2(0x7f7f7f7fu, 0x7f7f7f7fu);
+                if (sfsrc) sv = __ldcg(reinterpret_cast<const uint2*>(sfsrc + (size_t)kb * 8));
                 const uint32_t s = it % S;
                 if (it >= (uint32_t)S && alive)
                     alive = mbar_wait_bounded(smem_u32(&bar_empty[s]), ((it / S) - 1) & 1, 4);
-                uint8_t* stage = gemm_smem + s * L::kStageBytes;
+                const uint32_t stage = smem_u32(gemm_smem) + s * L::kStageBytes;
 #pragma unroll
                 for (int m = 0; m < MATS; ++m)
 #pragma unroll
                     for (int h = 0; h < 2; ++h)
-                        *reinterpret_cast<uint4*>(stage + m * kQTile + tc05_sw128_offset(wr[h], wc)) = wv[m][h];
+                        asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(stage + m * kQTile + tc05_sw128_offset(wr[h], wc)),
+                                     "l"(wsrc[m][h] + (size_t)kb * 128) : "memory");
 #pragma unroll
-                for (int t = 0; t < kQTerms; ++t)
+                for (int t = 0; t < kQTerms; ++t) {
+                    const int base_row = t == 2 ? term_row2 : t * n_mma;
 #pragma unroll
-                    for (int h = 0; h < 2; ++h)
-                        if (bwrite[h])
-                            *reinterpret_cast<uint4*>(stage + L::kOffB + t * kQTile + tc05_sw128_offset(wr[h], wc)) = bv[t][h];
-#pragma unroll
-                for (int h = 0; h < 2; ++h)
-                    if (sfok[h]) {
-                        // scales 0..3 -> atom 0, 4..7 -> atom 1; the four bytes of a row are one aligned word
-                        *reinterpret_cast<uint32_t*>(stage + sfdst[h] + tc05_scale_atom_offset(sf_row, 0)) = sv[h].x;
-                        *reinterpret_cast<uint32_t*>(stage + sfdst[h] + 512 + tc05_scale_atom_offset(sf_row, 0)) = sv[h].y;
-                    }
+                    for (int h = 0; h < kBChunks; ++h)
+                        if (bwrite[h])      // rows past the expert's tokens: source size 0 = zero fill
+                            asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(stage + L::kOffB + tc05_sw128_offset(base_row + wr[h], wc)),
+                                         "l"(bsrc[h] + (long long)t * a.act_rows * row_p + (size_t)kb * 128), "r"(bok[h] ? 16 : 0) : "memory");
+                }
+                if (sfok) {
+                    // scales 0..3 -> k-atom 0, 4..7 -> k-atom 1; the four bytes of a row are one aligned word
+                    asm volatile("st.shared.u32 [%0], %1;" ::"r"(stage + sfdst), "r"(sv.x) : "memory");
+                    asm volatile("st.shared.u32 [%0], %1;" ::"r"(stage + sfdst + sf_atom_stride), "r"(sv.y) : "memory");
+                }
                 asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-                __syncwarp();
-                if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(&bar_full[s])) : "memory");
+                asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(smem_u32(&bar_full[s])) : "memory");
             }
         } else {
             // ---- last warp: scale atoms into tensor memory, then the MMAs of the stage
+            const int n_first = split ? 2 * n_mma : 3 * n_mma;       // N of the first MMA
+            const int groups = (term_row2 + n_mma + 127) >> 7;       // row groups of B scales in use
             for (int kb = 0; kb < n_kb; ++kb, ++it) {
                 const uint32_t s = it % S;
                 if (alive) alive = mbar_wait_bounded(smem_u32(&bar_full[s]), (it / S) & 1, 5);
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // copies landed via the generic proxy
                 tc05_fence_after_sync();
                 if (lane == 0 && alive) {
                     const uint32_t stage = smem_u32(gemm_smem) + s * L::kStageBytes;
-                    const uint32_t sf_cols = tmem + L::kAccCols + s * L::kSfColsPerStage;   // [op][atom] x 4 columns
+                    const uint32_t sfa_cols = tmem + L::kAccCols + s * L::kSfColsPerStage;  // [mat][k-atom] x 4 columns
+                    const uint32_t sfb_cols = sfa_cols + L::kSfBCol;                        // [k-atom][row group] x 4
 #pragma unroll
-                    for (int op = 0; op < MATS + kQTerms; ++op)
+                    for (int at = 0; at < 2; ++at) {
 #pragma unroll
-                        for (int at = 0; at < 2; ++at)
-                            tc05_copy_scale_atom(sf_cols + op * 8 + at * 4,
-                                                 stage + (op < MATS ? L::kOffSfA + op * kQAtoms
-                                                                    : L::kOffSfB + (op - MATS) * kQAtoms) + at * 512);
+                        for (int m = 0; m < MATS; ++m)
+                            tc05_copy_scale_atom(sfa_cols + m * 8 + at * 4, stage + L::kOffSfA + m * 1024 + at * 512);
+#pragma unroll
+                        for (int g = 0; g < RG; ++g)
+                            if (g < groups)
+                                tc05_copy_scale_atom(sfb_cols + (at * RG + g) * 4, stage + L::kOffSfB + (at * RG + g) * 512);
+                    }
 #pragma unroll
                     for (int j = 0; j < 4; ++j) {                                           // K-steps of 64
-                        const uint32_t idesc = tc05_idesc_mxf4(128, n_mma, (j & 1) * 2, (j & 1) * 2);
+                        const uint32_t acc = (kb > 0 || j > 0) ? 1u : 0u;
+                        const uint32_t sfb = sfb_cols + (j >> 1) * RG * 4;
+                        const uint32_t idesc = tc05_idesc_mxf4(128, n_first, (j & 1) * 2, (j & 1) * 2);
+                        const uint64_t db = tc05_desc_k_sw128(stage + L::kOffB + 32 * j);
 #pragma unroll
-                        for (int t = 0; t < kQTerms; ++t) {
-                            const uint64_t db = tc05_desc_k_sw128(stage + L::kOffB + t * kQTile + 32 * j);
+                        for (int m = 0; m < MATS; ++m)
+                            tc05_mma_mxf4(tmem + m * L::kAccStride, tc05_desc_k_sw128(stage + m * kQTile + 32 * j), db,
+                                          idesc, sfa_cols + m * 8 + (j >> 1) * 4, sfb, acc);
+                        if (split) {
+                            const uint32_t idesc3 = tc05_idesc_mxf4(128, n_mma, (j & 1) * 2, (j & 1) * 2);
+                            const uint64_t db3 = tc05_desc_k_sw128(stage + L::kOffB + 256 * 128 + 32 * j);
 #pragma unroll
                             for (int m = 0; m < MATS; ++m)
-                                tc05_mma_mxf4(tmem + m * 128, tc05_desc_k_sw128(stage + m * kQTile + 32 * j), db, idesc,
-                                              sf_cols + m * 8 + (j >> 1) * 4, sf_cols + (MATS + t) * 8 + (j >> 1) * 4,
-                                              (kb > 0 || j > 0 || t > 0) ? 1u : 0u);
+                                tc05_mma_mxf4(tmem + m * L::kAccStride + 256,
+                                              tc05_desc_k_sw128(stage + m * kQTile + 32 * j), db3, idesc3,
+                                              sfa_cols + m * 8 + (j >> 1) * 4, sfb + 8, acc);
                         }
                     }
                     tc05_commit(smem_u32(&bar_empty[s]));
@@ -235,16 +258,31 @@ __global__ void __launch_bounds__(kGemmThreads, 1) moe_gemm_mxf4_kernel(const Mo
             }
         }
 
-        // ---- epilogue: warps 0..3 own accumulator rows 32 w .. 32 w + 31
+        // ---- epilogue: warps 0..3 own accumulator rows 32 w .. 32 w + 31; a token's value is the sum of its three
+        // term columns (added in term order)
         if (warp < 4) {
             if (alive) alive = mbar_wait_bounded(smem_u32(&bar_accum), tile_count & 1, 6);
             tc05_fence_after_sync();
             const int r = tid;
             const uint32_t trow = tmem + ((uint32_t)(warp * 32) << 16);
             for (int c0 = 0; c0 < n_mma && alive; c0 += 16) {
-                float g[16], u[16];
+                float g[16], u[16], part[16];
                 tc05_ld16(trow + c0, g);
-                if (MODE == 0) tc05_ld16(trow + 128 + c0, u);
+                tc05_ld16(trow + n_mma + c0, part);
+#pragma unroll
+                for (int i = 0; i < 16; ++i) g[i] += part[i];
+                tc05_ld16(trow + term_row2 + c0, part);
+#pragma unroll
+                for (int i = 0; i < 16; ++i) g[i] += part[i];
+                if (MODE == 0) {
+                    tc05_ld16(trow + L::kAccStride + c0, u);
+                    tc05_ld16(trow + L::kAccStride + n_mma + c0, part);
+#pragma unroll
+                    for (int i = 0; i < 16; ++i) u[i] += part[i];
+                    tc05_ld16(trow + L::kAccStride + term_row2 + c0, part);
+#pragma unroll
+                    for (int i = 0; i < 16; ++i) u[i] += part[i];
+                }
 #pragma unroll
                 for (int i = 0; i < 16; ++i) {
                     const int n = c0 + i;

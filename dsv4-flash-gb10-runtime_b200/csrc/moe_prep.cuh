@@ -8,7 +8,7 @@ namespace dsv4 {
 
 constexpr int kMoeMaxExperts = 1024;
 constexpr int kMoeTileRows = 128;      // weight rows per tensor-core tile (the MMA's M)
-constexpr int kMoeTileTokens = 128;    // tokens per tile at most (the MMA's N)
+constexpr int kMoeTileTokens = 128;    // tokens per tile at most (fp16 path; the MMA's N)
 
 // Work descriptors written by the grouping kernel, read by the GEMM kernels.
 struct MoeGroups {
@@ -54,10 +54,11 @@ __global__ void moe_token_fp16_kernel(const __nv_bfloat16* __restrict__ x, int n
 }
 
 // Single CTA: counting sort of the P = n_tokens * k pairs by expert id.  The order of pairs inside an expert is
-// arbitrary (it only decides which accumulator column a token uses, not any arithmetic).
+// arbitrary (it only decides which accumulator column a token uses, not any arithmetic).  tok_up / tok_down:
+// tokens per gate/up and per down tile of the GEMM kernels that will read the tables.
 __global__ void __launch_bounds__(1024) moe_group_kernel(const int* __restrict__ ids, int n_pairs, int n_experts,
-                                                         int rows_up, int rows_down, MoeGroups g,
-                                                         int* __restrict__ status) {
+                                                         int rows_up, int rows_down, int tok_up, int tok_down,
+                                                         MoeGroups g, int* __restrict__ status) {
     __shared__ int count[kMoeMaxExperts];
     __shared__ int cursor[kMoeMaxExperts];
     pdl_launch_dependents();
@@ -75,10 +76,9 @@ __global__ void __launch_bounds__(1024) moe_group_kernel(const int* __restrict__
         for (int e = 0; e < n_experts; ++e) {
             g.offsets[e] = off; g.tiles_up[e] = tu; g.tiles_down[e] = td;
             cursor[e] = off;
-            const int n_tiles = (count[e] + kMoeTileTokens - 1) / kMoeTileTokens;
             off += count[e];
-            tu += n_tiles * (rows_up / kMoeTileRows);
-            td += n_tiles * (rows_down / kMoeTileRows);
+            tu += ((count[e] + tok_up - 1) / tok_up) * (rows_up / kMoeTileRows);
+            td += ((count[e] + tok_down - 1) / tok_down) * (rows_down / kMoeTileRows);
         }
         g.offsets[n_experts] = off; g.tiles_up[n_experts] = tu; g.tiles_down[n_experts] = td;
     }
