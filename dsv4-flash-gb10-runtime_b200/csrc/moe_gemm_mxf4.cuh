@@ -17,7 +17,10 @@
 // the 16 producer warps copy with cp.async: the packed weight rows, the three packed activation terms of the
 // tile's tokens, and the scale bytes re-arranged into 512-byte scale atoms; one lane of the last warp copies the
 // atoms into tensor memory (tcgen05.cp) and issues the MMAs; tcgen05.commit releases the stage.  Persistent grid,
-// one CTA per SM.  Every wait is bounded.
+// one CTA per SM.  Producers and the MMA warp run ahead across tile boundaries: the producers start filling the
+// stages of the next tile while the last MMAs of the current one are in flight, then (all 16 warps, four per lane
+// quadrant of tensor memory) drain the finished accumulator and hand it back to the MMA warp through an mbarrier.
+// Every wait is bounded.
 #pragma once
 
 #include "moe_gemm.cuh"
@@ -68,6 +71,33 @@ struct MoeQGemmLayout {
     static_assert(kBytes <= 227 * 1024, "shared memory overflow");
 };
 
+// What a tile is: expert, rows, tokens; identical in every thread of the CTA.
+struct MoeQTile {
+    int e, slot0, n_valid, n_mma, m0, term_row2;
+    bool split;
+};
+
+template <int TOK>
+__device__ __forceinline__ MoeQTile moe_qtile_decode(const int* __restrict__ tiles, const int* __restrict__ offsets,
+                                                     int n_experts, int m_tiles, int tile) {
+    int lo = 0, hi = n_experts;
+    while (hi - lo > 1) {
+        const int md = (lo + hi) >> 1;
+        if (tiles[md] <= tile) lo = md; else hi = md;
+    }
+    MoeQTile t;
+    t.e = lo;
+    const int local = tile - tiles[lo];
+    const int nt = local / m_tiles, mt = local - nt * m_tiles;
+    t.slot0 = offsets[lo] + nt * TOK;
+    t.n_valid = min(TOK, offsets[lo + 1] - t.slot0);
+    t.n_mma = (t.n_valid + 15) & ~15;
+    t.m0 = mt * kMoeTileRows;
+    t.split = 3 * t.n_mma > 256;                       // B rows (= accumulator columns) of the three terms
+    t.term_row2 = t.split ? 256 : 2 * t.n_mma;
+    return t;
+}
+
 template <int MODE>
 __global__ void __launch_bounds__(kGemmThreads, 1) moe_gemm_mxf4_kernel(const MoeQGemmArgs a) {
     using L = MoeQGemmLayout<MODE>;
@@ -78,10 +108,10 @@ __global__ void __launch_bounds__(kGemmThreads, 1) moe_gemm_mxf4_kernel(const Mo
     constexpr int kProducerWarps = kGemmProducers / 32;
     constexpr int kBChunks = (TOK * 8 + kGemmProducers - 1) / kGemmProducers;   // 16-byte chunks per thread and term
     extern __shared__ __align__(1024) uint8_t gemm_smem[];
-    __shared__ __align__(8) uint64_t bar_full[S], bar_empty[S], bar_accum;
+    __shared__ __align__(8) uint64_t bar_full[S], bar_empty[S], bar_accum, bar_acc_free;
     __shared__ uint32_t tmem_holder;
-    __shared__ int tok_row[128];             // activation row of every token of the tile
-    __shared__ float tok_w[128];             // router weight of every token (down)
+    __shared__ int tok_row[2][128];          // activation row of every token of the tile (by tile parity)
+    __shared__ float tok_w[2][128];          // router weight of every token (down)
     pdl_launch_dependents();
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -93,6 +123,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) moe_gemm_mxf4_kernel(const Mo
     if (tid == 0) {
         for (int s = 0; s < S; ++s) { mbar_init(smem_u32(&bar_full[s]), kGemmProducers); mbar_init(smem_u32(&bar_empty[s]), 1); }
         mbar_init(smem_u32(&bar_accum), 1);
+        mbar_init(smem_u32(&bar_acc_free), kGemmProducers);
         mbar_init_fence();
     }
     pdl_wait();
@@ -107,29 +138,63 @@ __global__ void __launch_bounds__(kGemmThreads, 1) moe_gemm_mxf4_kernel(const Mo
     uint32_t it = 0, tile_count = 0;
     bool alive = true;
 
-    for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x, ++tile_count) {
-        int lo = 0, hi = a.n_experts;
-        while (hi - lo > 1) {
-            const int md = (lo + hi) >> 1;
-            if (tiles[md] <= tile) lo = md; else hi = md;
-        }
-        const int e = lo;
-        const int local = tile - tiles[e];
-        const int nt = local / m_tiles, mt = local - nt * m_tiles;
-        const int slot0 = a.g.offsets[e] + nt * TOK;
-        const int n_valid = min(TOK, a.g.offsets[e + 1] - slot0);
-        const int n_mma = (n_valid + 15) & ~15;
-        const int m0 = mt * kMoeTileRows;
-        // B rows (= accumulator columns) of the three terms
-        const bool split = 3 * n_mma > 256;
-        const int term_row2 = split ? 256 : 2 * n_mma;
+    if (producer) {
+        // ---- drain of a finished accumulator: warps q, q + 4, q + 8, q + 12 own lane quadrant q (rows 32 q ..)
+        // and share its token chunks of 16; a token's value is the sum of its three term columns (term order)
+        auto drain = [&](const MoeQTile& t, uint32_t count) {
+            if (alive) alive = mbar_wait_bounded(smem_u32(&bar_accum), count & 1, 6);
+            tc05_fence_after_sync();
+            const int quad = warp & 3;
+            const int r = quad * 32 + lane;
+            const uint32_t trow = tmem + ((uint32_t)(quad * 32) << 16);
+            const int* rows_of = tok_row[count & 1];
+            const float* w_of = tok_w[count & 1];
+            (void)rows_of;
+            for (int c0 = (warp >> 2) * 16; c0 < t.n_mma && alive; c0 += 64) {
+                float g[16], u[16], part[16];
+                tc05_ld16(trow + c0, g);
+                tc05_ld16(trow + t.n_mma + c0, part);
+#pragma unroll
+                for (int i = 0; i < 16; ++i) g[i] += part[i];
+                tc05_ld16(trow + t.term_row2 + c0, part);
+#pragma unroll
+                for (int i = 0; i < 16; ++i) g[i] += part[i];
+                if (MODE == 0) {
+                    tc05_ld16(trow + L::kAccStride + c0, u);
+                    tc05_ld16(trow + L::kAccStride + t.n_mma + c0, part);
+#pragma unroll
+                    for (int i = 0; i < 16; ++i) u[i] += part[i];
+                    tc05_ld16(trow + L::kAccStride + t.term_row2 + c0, part);
+#pragma unroll
+                    for (int i = 0; i < 16; ++i) u[i] += part[i];
+                }
+#pragma unroll
+                for (int i = 0; i < 16; ++i) {
+                    const int n = c0 + i;
+                    if (n < t.n_valid) {
+                        if (MODE == 0)
+                            a.mid[(size_t)(t.slot0 + n) * a.rows + t.m0 + r] = (g[i] / (1.0f + __expf(-g[i]))) * u[i];
+                        else
+                            a.y[(size_t)(t.slot0 + n) * a.rows + t.m0 + r] = g[i] * w_of[n];
+                    }
+                }
+            }
+            // accumulator (and this tile's token tables) free again
+            tc05_fence_before_sync();
+            asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(&bar_acc_free)) : "memory");
+        };
 
-        if (producer) {
-            if (tid < n_valid) {
-                const int slot = slot0 + tid;
+        MoeQTile prev;
+        bool has_prev = false;
+        const int drain_at = min(S, n_kb) - 1;        // the stage after whose issue the previous tile is drained
+        for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x, ++tile_count) {
+            const MoeQTile t = moe_qtile_decode<TOK>(tiles, a.g.offsets, a.n_experts, m_tiles, tile);
+            int* rows_of = tok_row[tile_count & 1];
+            if (tid < t.n_valid) {
+                const int slot = t.slot0 + tid;
                 const int pair = a.g.slot_pair[slot];
-                tok_row[tid] = MODE == 0 ? pair / a.k_top : slot;
-                if (MODE == 1) tok_w[tid] = a.pair_w[pair];
+                rows_of[tid] = MODE == 0 ? pair / a.k_top : slot;
+                if (MODE == 1) tok_w[tile_count & 1][tid] = a.pair_w[pair];
             }
             asm volatile("bar.sync 1, %0;" ::"n"(kGemmProducers) : "memory");
 
@@ -142,15 +207,15 @@ __global__ void __launch_bounds__(kGemmThreads, 1) moe_gemm_mxf4_kernel(const Mo
             for (int m = 0; m < MATS; ++m)
 #pragma unroll
                 for (int h = 0; h < 2; ++h)
-                    wsrc[m][h] = (m == 0 ? a.wa_p : a.wb_p) + e * a.stride_p + (long long)(m0 + wr[h]) * row_p + wc * 16;
+                    wsrc[m][h] = (m == 0 ? a.wa_p : a.wb_p) + t.e * a.stride_p + (long long)(t.m0 + wr[h]) * row_p + wc * 16;
             // activations: chunk (token, c) of each term
             const uint8_t* bsrc[kBChunks];
             bool bok[kBChunks], bwrite[kBChunks];
 #pragma unroll
             for (int h = 0; h < kBChunks; ++h) {
-                bok[h] = wr[h] < n_valid;
-                bwrite[h] = wr[h] < n_mma;
-                bsrc[h] = a.act_q + (long long)(bok[h] ? tok_row[wr[h]] : 0) * row_p + wc * 16;
+                bok[h] = wr[h] < t.n_valid;
+                bwrite[h] = wr[h] < t.n_mma;
+                bsrc[h] = a.act_q + (long long)(bok[h] ? rows_of[wr[h]] : 0) * row_p + wc * 16;
             }
             // scales: one row of 8 bytes per thread; threads [0, 128 MATS) the weight rows, then TOK per term
             const uint8_t* sfsrc = nullptr;
@@ -158,18 +223,18 @@ __global__ void __launch_bounds__(kGemmThreads, 1) moe_gemm_mxf4_kernel(const Mo
             bool sfok = false;
             if (tid < MATS * 128) {
                 const int m = tid >> 7, r = tid & 127;
-                sfsrc = (m == 0 ? a.wa_s : a.wb_s) + e * a.stride_s + (long long)(m0 + r) * row_s;
+                sfsrc = (m == 0 ? a.wa_s : a.wb_s) + t.e * a.stride_s + (long long)(t.m0 + r) * row_s;
                 sfdst = L::kOffSfA + m * 1024 + tc05_scale_atom_offset(r, 0);
                 sfok = true;
             } else if (tid < MATS * 128 + kQTerms * TOK) {
                 const int idx = tid - MATS * 128;
-                const int t = idx / TOK, n = idx - t * TOK;
-                if (n < n_mma) {
-                    const int brow = (t == 2 ? term_row2 : t * n_mma) + n;
+                const int term = idx / TOK, n = idx - term * TOK;
+                if (n < t.n_mma) {
+                    const int brow = (term == 2 ? t.term_row2 : term * t.n_mma) + n;
                     sfok = true;
                     sfdst = L::kOffSfB + (brow >> 7) * 512 + tc05_scale_atom_offset(brow & 127, 0);
-                    if (n < n_valid)                                  // padding rows: scale 1, data 0
-                        sfsrc = a.act_s + (long long)t * a.act_rows * row_s + (long long)tok_row[n] * row_s;
+                    if (n < t.n_valid)                                // padding rows: scale 1, data 0
+                        sfsrc = a.act_s + (long long)term * a.act_rows * row_s + (long long)rows_of[n] * row_s;
                 }
             }
             const uint32_t sf_atom_stride = tid < MATS * 128 ? 512u : (uint32_t)RG * 512u;   // k-atom 0 -> 1
@@ -192,13 +257,13 @@ __global__ void __launch_bounds__(kGemmThreads, 1) moe_gemm_mxf4_kernel(const Mo
                         asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(stage + m * kQTile + tc05_sw128_offset(wr[h], wc)),
                                      "l"(wsrc[m][h] + (size_t)kb * 128) : "memory");
 #pragma unroll
-                for (int t = 0; t < kQTerms; ++t) {
-                    const int base_row = t == 2 ? term_row2 : t * n_mma;
+                for (int term = 0; term < kQTerms; ++term) {
+                    const int base_row = term == 2 ? t.term_row2 : term * t.n_mma;
 #pragma unroll
                     for (int h = 0; h < kBChunks; ++h)
                         if (bwrite[h])      // rows past the expert's tokens: source size 0 = zero fill
                             asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(stage + L::kOffB + tc05_sw128_offset(base_row + wr[h], wc)),
-                                         "l"(bsrc[h] + (long long)t * a.act_rows * row_p + (size_t)kb * 128), "r"(bok[h] ? 16 : 0) : "memory");
+                                         "l"(bsrc[h] + (long long)term * a.act_rows * row_p + (size_t)kb * 128), "r"(bok[h] ? 16 : 0) : "memory");
                 }
                 if (sfok) {
                     // scales 0..3 -> k-atom 0, 4..7 -> k-atom 1; the four bytes of a row are one aligned word
@@ -207,11 +272,21 @@ __global__ void __launch_bounds__(kGemmThreads, 1) moe_gemm_mxf4_kernel(const Mo
                 }
                 asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
                 asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(smem_u32(&bar_full[s])) : "memory");
+                // the first stages of this tile are on their way: now drain the previous tile's accumulator
+                if (kb == drain_at && has_prev) drain(prev, tile_count - 1);
             }
-        } else {
-            // ---- last warp: scale atoms into tensor memory, then the MMAs of the stage
-            const int n_first = split ? 2 * n_mma : 3 * n_mma;       // N of the first MMA
-            const int groups = (term_row2 + n_mma + 127) >> 7;       // row groups of B scales in use
+            prev = t;
+            has_prev = true;
+        }
+        if (has_prev) drain(prev, tile_count - 1);
+    } else {
+        // ---- last warp: scale atoms into tensor memory, then the MMAs of the stage
+        for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x, ++tile_count) {
+            const MoeQTile t = moe_qtile_decode<TOK>(tiles, a.g.offsets, a.n_experts, m_tiles, tile);
+            const int n_first = t.split ? 2 * t.n_mma : 3 * t.n_mma;     // N of the first MMA
+            const int groups = (t.term_row2 + t.n_mma + 127) >> 7;       // row groups of B scales in use
+            if (tile_count > 0 && alive)                                 // previous accumulator drained?
+                alive = mbar_wait_bounded(smem_u32(&bar_acc_free), (tile_count - 1) & 1, 7);
             for (int kb = 0; kb < n_kb; ++kb, ++it) {
                 const uint32_t s = it % S;
                 if (alive) alive = mbar_wait_bounded(smem_u32(&bar_full[s]), (it / S) & 1, 5);
@@ -241,8 +316,8 @@ __global__ void __launch_bounds__(kGemmThreads, 1) moe_gemm_mxf4_kernel(const Mo
                         for (int m = 0; m < MATS; ++m)
                             tc05_mma_mxf4(tmem + m * L::kAccStride, tc05_desc_k_sw128(stage + m * kQTile + 32 * j), db,
                                           idesc, sfa_cols + m * 8 + (j >> 1) * 4, sfb, acc);
-                        if (split) {
-                            const uint32_t idesc3 = tc05_idesc_mxf4(128, n_mma, (j & 1) * 2, (j & 1) * 2);
+                        if (t.split) {
+                            const uint32_t idesc3 = tc05_idesc_mxf4(128, t.n_mma, (j & 1) * 2, (j & 1) * 2);
                             const uint64_t db3 = tc05_desc_k_sw128(stage + L::kOffB + 256 * 128 + 32 * j);
 #pragma unroll
                             for (int m = 0; m < MATS; ++m)
@@ -257,48 +332,8 @@ __global__ void __launch_bounds__(kGemmThreads, 1) moe_gemm_mxf4_kernel(const Mo
                 __syncwarp();
             }
         }
-
-        // ---- epilogue: warps 0..3 own accumulator rows 32 w .. 32 w + 31; a token's value is the sum of its three
-        // term columns (added in term order)
-        if (warp < 4) {
-            if (alive) alive = mbar_wait_bounded(smem_u32(&bar_accum), tile_count & 1, 6);
-            tc05_fence_after_sync();
-            const int r = tid;
-            const uint32_t trow = tmem + ((uint32_t)(warp * 32) << 16);
-            for (int c0 = 0; c0 < n_mma && alive; c0 += 16) {
-                float g[16], u[16], part[16];
-                tc05_ld16(trow + c0, g);
-                tc05_ld16(trow + n_mma + c0, part);
-#pragma unroll
-                for (int i = 0; i < 16; ++i) g[i] += part[i];
-                tc05_ld16(trow + term_row2 + c0, part);
-#pragma unroll
-                for (int i = 0; i < 16; ++i) g[i] += part[i];
-                if (MODE == 0) {
-                    tc05_ld16(trow + L::kAccStride + c0, u);
-                    tc05_ld16(trow + L::kAccStride + n_mma + c0, part);
-#pragma unroll
-                    for (int i = 0; i < 16; ++i) u[i] += part[i];
-                    tc05_ld16(trow + L::kAccStride + term_row2 + c0, part);
-#pragma unroll
-                    for (int i = 0; i < 16; ++i) u[i] += part[i];
-                }
-#pragma unroll
-                for (int i = 0; i < 16; ++i) {
-                    const int n = c0 + i;
-                    if (n < n_valid) {
-                        if (MODE == 0)
-                            a.mid[(size_t)(slot0 + n) * a.rows + m0 + r] = (g[i] / (1.0f + __expf(-g[i]))) * u[i];
-                        else
-                            a.y[(size_t)(slot0 + n) * a.rows + m0 + r] = g[i] * tok_w[n];
-                    }
-                }
-            }
-        }
-        tc05_fence_before_sync();
-        __syncthreads();
-        tc05_fence_after_sync();
     }
+    tc05_fence_before_sync();
     __syncthreads();
     if (warp == kProducerWarps) tc05_dealloc(tmem, 512);
 }
