@@ -77,9 +77,10 @@ struct MoeQTile {
     bool split;
 };
 
+// tiles / offsets: the grouping kernel's prefix sums, staged in shared memory by the caller.
 template <int TOK>
-__device__ __forceinline__ MoeQTile moe_qtile_decode(const int* __restrict__ tiles, const int* __restrict__ offsets,
-                                                     int n_experts, int m_tiles, int tile) {
+__device__ __forceinline__ MoeQTile moe_qtile_decode(const int* tiles, const int* offsets, int n_experts, int m_tiles,
+                                                     int tile) {
     int lo = 0, hi = n_experts;
     while (hi - lo > 1) {
         const int md = (lo + hi) >> 1;
@@ -112,6 +113,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) moe_gemm_mxf4_kernel(const Mo
     __shared__ uint32_t tmem_holder;
     __shared__ int tok_row[2][128];          // activation row of every token of the tile (by tile parity)
     __shared__ float tok_w[2][128];          // router weight of every token (down)
+    __shared__ int s_tiles[kMoeMaxExperts + 1], s_offsets[kMoeMaxExperts + 1];
     pdl_launch_dependents();
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -127,12 +129,16 @@ __global__ void __launch_bounds__(kGemmThreads, 1) moe_gemm_mxf4_kernel(const Mo
         mbar_init_fence();
     }
     pdl_wait();
+    for (int i = tid; i <= a.n_experts; i += kGemmThreads) {
+        s_tiles[i] = (MODE == 0 ? a.g.tiles_up : a.g.tiles_down)[i];
+        s_offsets[i] = a.g.offsets[i];
+    }
     tc05_fence_before_sync();
     __syncthreads();
     tc05_fence_after_sync();
     const uint32_t tmem = tmem_holder;
 
-    const int* tiles = MODE == 0 ? a.g.tiles_up : a.g.tiles_down;
+    const int* tiles = s_tiles;
     const int n_tiles = tiles[a.n_experts];
     const int m_tiles = a.rows / kMoeTileRows;
     uint32_t it = 0, tile_count = 0;
@@ -147,26 +153,37 @@ __global__ void __launch_bounds__(kGemmThreads, 1) moe_gemm_mxf4_kernel(const Mo
             const int quad = warp & 3;
             const int r = quad * 32 + lane;
             const uint32_t trow = tmem + ((uint32_t)(quad * 32) << 16);
-            const int* rows_of = tok_row[count & 1];
             const float* w_of = tok_w[count & 1];
-            (void)rows_of;
+            bool handed_back = false;
             for (int c0 = (warp >> 2) * 16; c0 < t.n_mma && alive; c0 += 64) {
-                float g[16], u[16], part[16];
-                tc05_ld16(trow + c0, g);
-                tc05_ld16(trow + t.n_mma + c0, part);
+                // the three term columns of 16 tokens in flight together, one wait
+                uint32_t p0[16], p1[16], p2[16];
+                float g[16], u[16];
+                tc05_ld16_issue(trow + c0, p0);
+                tc05_ld16_issue(trow + t.n_mma + c0, p1);
+                tc05_ld16_issue(trow + t.term_row2 + c0, p2);
+                tc05_wait_ld();
 #pragma unroll
-                for (int i = 0; i < 16; ++i) g[i] += part[i];
-                tc05_ld16(trow + t.term_row2 + c0, part);
-#pragma unroll
-                for (int i = 0; i < 16; ++i) g[i] += part[i];
+                for (int i = 0; i < 16; ++i)
+                    g[i] = (__uint_as_float(p0[i]) + __uint_as_float(p1[i])) + __uint_as_float(p2[i]);
                 if (MODE == 0) {
-                    tc05_ld16(trow + L::kAccStride + c0, u);
-                    tc05_ld16(trow + L::kAccStride + t.n_mma + c0, part);
+                    tc05_ld16_issue(trow + L::kAccStride + c0, p0);
+                    tc05_ld16_issue(trow + L::kAccStride + t.n_mma + c0, p1);
+                    tc05_ld16_issue(trow + L::kAccStride + t.term_row2 + c0, p2);
+                    tc05_wait_ld();
 #pragma unroll
-                    for (int i = 0; i < 16; ++i) u[i] += part[i];
-                    tc05_ld16(trow + L::kAccStride + t.term_row2 + c0, part);
+                    for (int i = 0; i < 16; ++i)
+                        u[i] = (__uint_as_float(p0[i]) + __uint_as_float(p1[i])) + __uint_as_float(p2[i]);
+                } else {
 #pragma unroll
-                    for (int i = 0; i < 16; ++i) u[i] += part[i];
+                    for (int i = 0; i < 16; ++i) u[i] = c0 + i < t.n_valid ? w_of[c0 + i] : 0.f;
+                }
+                if (c0 + 64 >= t.n_mma) {
+                    // this thread's last read of the accumulator and of the token tables: hand both back to the
+                    // MMA warp before the stores
+                    tc05_fence_before_sync();
+                    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(&bar_acc_free)) : "memory");
+                    handed_back = true;
                 }
 #pragma unroll
                 for (int i = 0; i < 16; ++i) {
@@ -175,20 +192,21 @@ __global__ void __launch_bounds__(kGemmThreads, 1) moe_gemm_mxf4_kernel(const Mo
                         if (MODE == 0)
                             a.mid[(size_t)(t.slot0 + n) * a.rows + t.m0 + r] = (g[i] / (1.0f + __expf(-g[i]))) * u[i];
                         else
-                            a.y[(size_t)(t.slot0 + n) * a.rows + t.m0 + r] = g[i] * w_of[n];
+                            a.y[(size_t)(t.slot0 + n) * a.rows + t.m0 + r] = g[i] * u[i];
                     }
                 }
             }
-            // accumulator (and this tile's token tables) free again
-            tc05_fence_before_sync();
-            asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(&bar_acc_free)) : "memory");
+            if (!handed_back) {
+                tc05_fence_before_sync();
+                asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(&bar_acc_free)) : "memory");
+            }
         };
 
         MoeQTile prev;
         bool has_prev = false;
         const int drain_at = min(S, n_kb) - 1;        // the stage after whose issue the previous tile is drained
         for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x, ++tile_count) {
-            const MoeQTile t = moe_qtile_decode<TOK>(tiles, a.g.offsets, a.n_experts, m_tiles, tile);
+            const MoeQTile t = moe_qtile_decode<TOK>(tiles, s_offsets, a.n_experts, m_tiles, tile);
             int* rows_of = tok_row[tile_count & 1];
             if (tid < t.n_valid) {
                 const int slot = t.slot0 + tid;
@@ -282,7 +300,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) moe_gemm_mxf4_kernel(const Mo
     } else {
         // ---- last warp: scale atoms into tensor memory, then the MMAs of the stage
         for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x, ++tile_count) {
-            const MoeQTile t = moe_qtile_decode<TOK>(tiles, a.g.offsets, a.n_experts, m_tiles, tile);
+            const MoeQTile t = moe_qtile_decode<TOK>(tiles, s_offsets, a.n_experts, m_tiles, tile);
             const int n_first = t.split ? 2 * t.n_mma : 3 * t.n_mma;     // N of the first MMA
             const int groups = (t.term_row2 + t.n_mma + 127) >> 7;       // row groups of B scales in use
             if (tile_count > 0 && alive)                                 // previous accumulator drained?

@@ -65,10 +65,20 @@ __global__ void __launch_bounds__(1024) moe_group_kernel(const int* __restrict__
     pdl_wait();
     for (int e = threadIdx.x; e < n_experts; e += blockDim.x) count[e] = 0;
     __syncthreads();
-    for (int p = threadIdx.x; p < n_pairs; p += blockDim.x) {
-        const int e = ids[p];
-        if (e >= 0 && e < n_experts) atomicAdd(&count[e], 1);
-        else atomicExch(status, 3);                      // expert id out of range: the pair is dropped
+    // a single CTA is latency-bound: keep eight independent loads of ids in flight per thread
+    constexpr int kBatch = 8;
+    for (int p0 = threadIdx.x; p0 < n_pairs; p0 += blockDim.x * kBatch) {
+        int e[kBatch];
+#pragma unroll
+        for (int i = 0; i < kBatch; ++i) {
+            const int p = p0 + i * blockDim.x;
+            e[i] = p < n_pairs ? __ldg(ids + p) : -2;
+        }
+#pragma unroll
+        for (int i = 0; i < kBatch; ++i) {
+            if (e[i] >= 0 && e[i] < n_experts) atomicAdd(&count[e[i]], 1);
+            else if (e[i] != -2) atomicExch(status, 3);  // expert id out of range: the pair is dropped
+        }
     }
     __syncthreads();
     if (threadIdx.x == 0) {
@@ -83,14 +93,23 @@ __global__ void __launch_bounds__(1024) moe_group_kernel(const int* __restrict__
         g.offsets[n_experts] = off; g.tiles_up[n_experts] = tu; g.tiles_down[n_experts] = td;
     }
     __syncthreads();
-    for (int p = threadIdx.x; p < n_pairs; p += blockDim.x) {
-        const int e = ids[p];
-        if (e >= 0 && e < n_experts) {
-            const int slot = atomicAdd(&cursor[e], 1);
-            g.slot_pair[slot] = p;
-            g.pair_slot[p] = slot;
-        } else {
-            g.pair_slot[p] = -1;
+    for (int p0 = threadIdx.x; p0 < n_pairs; p0 += blockDim.x * kBatch) {
+        int e[kBatch];
+#pragma unroll
+        for (int i = 0; i < kBatch; ++i) {
+            const int p = p0 + i * blockDim.x;
+            e[i] = p < n_pairs ? __ldg(ids + p) : -2;
+        }
+#pragma unroll
+        for (int i = 0; i < kBatch; ++i) {
+            const int p = p0 + i * blockDim.x;
+            if (e[i] >= 0 && e[i] < n_experts) {
+                const int slot = atomicAdd(&cursor[e[i]], 1);
+                g.slot_pair[slot] = p;
+                g.pair_slot[p] = slot;
+            } else if (e[i] != -2) {
+                g.pair_slot[p] = -1;
+            }
         }
     }
 }
@@ -123,46 +142,60 @@ __global__ void moe_combine_kernel(const float* __restrict__ y, const int* __res
 // each term the round-to-nearest E2M1 quantisation of the residual the previous terms left.  The tensor cores
 // multiply FP4 by FP4; three terms are what keeps the layer inside its tolerance (one term: cosine 0.993).
 // Output: q [3][rows][K / 2] packed (low nibble = even element), s [3][rows][K / 32] E8M0 bytes.
-// A lane owns two neighbouring elements, 16 lanes own a block, a warp two blocks.
+// A lane owns eight neighbouring elements, four lanes own a block, a warp 256 consecutive elements of a row
+// (K must be a multiple of 256): 16- or 32-byte loads, one 4-byte store per lane and term.
 template <class Elem>
 __global__ void moe_quantize_mxfp4x3_kernel(const Elem* __restrict__ src, long long rows, int K,
                                             uint8_t* __restrict__ q, uint8_t* __restrict__ s) {
     pdl_launch_dependents();
     pdl_wait();
     const int lane = threadIdx.x & 31;
-    const long long n_pairs = rows * (K / 64);                      // a warp handles 64 consecutive elements
+    const long long n_chunks = rows * (K / 256);
     const long long term_q = rows * (K / 2), term_s = rows * (K / 32);
-    for (long long w = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); w < n_pairs;
+    for (long long w = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); w < n_chunks;
          w += (long long)gridDim.x * (blockDim.x >> 5)) {
-        const long long e0 = w * 64 + 2 * lane;                     // first of this lane's two elements (row-major)
-        float v0, v1;
+        const long long e0 = w * 256 + 8 * lane;                    // first of this lane's eight elements (row-major)
+        float v[8];
         if constexpr (sizeof(Elem) == 2) {
-            const uint32_t u = *reinterpret_cast<const uint32_t*>(src + e0);
-            v0 = __uint_as_float(u << 16);
-            v1 = __uint_as_float(u & 0xffff0000u);
+            const uint4 u = __ldcs(reinterpret_cast<const uint4*>(src + e0));
+            const uint32_t uu[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                v[2 * i] = __uint_as_float(uu[i] << 16);
+                v[2 * i + 1] = __uint_as_float(uu[i] & 0xffff0000u);
+            }
         } else {
-            const float2 f = *reinterpret_cast<const float2*>(src + e0);
-            v0 = f.x; v1 = f.y;
+            const float4 f0 = __ldcs(reinterpret_cast<const float4*>(src + e0));
+            const float4 f1 = __ldcs(reinterpret_cast<const float4*>(src + e0) + 1);
+            v[0] = f0.x; v[1] = f0.y; v[2] = f0.z; v[3] = f0.w;
+            v[4] = f1.x; v[5] = f1.y; v[6] = f1.z; v[7] = f1.w;
         }
 #pragma unroll
         for (int t = 0; t < 3; ++t) {
-            uint32_t m = max(__float_as_uint(v0) & 0x7fffffffu, __float_as_uint(v1) & 0x7fffffffu);
+            uint32_t m = 0;
 #pragma unroll
-            for (int off = 8; off > 0; off >>= 1) m = max(m, __shfl_xor_sync(kFullMask, m, off));   // 16-lane block
+            for (int i = 0; i < 8; ++i) m = max(m, __float_as_uint(v[i]) & 0x7fffffffu);
+            m = max(m, __shfl_xor_sync(kFullMask, m, 1));
+            m = max(m, __shfl_xor_sync(kFullMask, m, 2));            // 4-lane block
             int e = (int)(m >> 23) - 127 - 2;                       // amax / 2^e in [4, 8)
             if ((m & 0x007fffffu) > 0x00400000u) e += 1;             // above 6 * 2^e the E2M1 grid would saturate
             e = min(max(e, -127), 127);
             if (m == 0) e = -127;
             const float inv = __uint_as_float((uint32_t)min(max(127 - e, 1), 254) << 23);
             const float sc = __uint_as_float((uint32_t)max(e + 127, 1) << 23);                     // 2^e (>= 2^-126)
-            uint16_t packed;
-            asm("{\n .reg .b8 b;\n cvt.rn.satfinite.e2m1x2.f32 b, %2, %1;\n mov.b16 %0, {b, 0};\n}"
-                : "=h"(packed) : "f"(v0 * inv), "f"(v1 * inv));
-            const float2 back = e2m1x2_to_float2(packed);
-            v0 -= back.x * sc;
-            v1 -= back.y * sc;
-            q[t * term_q + (e0 >> 1)] = (uint8_t)packed;
-            if ((lane & 15) == 0) s[t * term_s + (e0 >> 5)] = (uint8_t)(e + 127);
+            uint32_t word = 0;
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                uint16_t packed;
+                asm("{\n .reg .b8 b;\n cvt.rn.satfinite.e2m1x2.f32 b, %2, %1;\n mov.b16 %0, {b, 0};\n}"
+                    : "=h"(packed) : "f"(v[2 * i] * inv), "f"(v[2 * i + 1] * inv));
+                const float2 back = e2m1x2_to_float2(packed);
+                v[2 * i] -= back.x * sc;
+                v[2 * i + 1] -= back.y * sc;
+                word |= (uint32_t)(packed & 0xff) << (8 * i);
+            }
+            *reinterpret_cast<uint32_t*>(q + t * term_q + (e0 >> 1)) = word;
+            if ((lane & 3) == 0) s[t * term_s + (e0 >> 5)] = (uint8_t)(e + 127);
         }
     }
 }

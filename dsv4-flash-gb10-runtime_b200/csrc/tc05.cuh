@@ -77,6 +77,16 @@ __device__ __forceinline__ void tc05_ld16(uint32_t taddr, float (&v)[16]) {
     for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
 }
 
+// The same without the wait: several loads can be in flight before one tc05_wait_ld().
+__device__ __forceinline__ void tc05_ld16_issue(uint32_t taddr, uint32_t (&r)[16]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+        : "r"(taddr));
+}
+__device__ __forceinline__ void tc05_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
 // Byte offset of 16-byte chunk `chunk` (0..7) of row `row` inside a K-major 128-byte-swizzled tile.
 __device__ __forceinline__ uint32_t tc05_sw128_offset(int row, int chunk) {
     return (uint32_t)row * 128u + (uint32_t)((chunk ^ (row & 7)) << 4);
