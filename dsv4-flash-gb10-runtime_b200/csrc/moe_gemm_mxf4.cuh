@@ -69,6 +69,7 @@ struct MoeQGemmLayout {
     static_assert(kAccCols + kStages * kSfColsPerStage <= 512, "tensor memory overflow");
     static_assert(kMats * 128 + kQTerms * kTok <= kGemmProducers, "one scale row per producer thread");
     static_assert(kBytes <= 227 * 1024, "shared memory overflow");
+    static_assert(kTok <= 128, "the drain handles at most two 16-token chunks per warp");
 };
 
 // What a tile is: expert, rows, tokens; identical in every thread of the CTA.
@@ -154,51 +155,57 @@ __global__ void __launch_bounds__(kGemmThreads, 1) moe_gemm_mxf4_kernel(const Mo
             const int r = quad * 32 + lane;
             const uint32_t trow = tmem + ((uint32_t)(quad * 32) << 16);
             const float* w_of = tok_w[count & 1];
-            bool handed_back = false;
-            for (int c0 = (warp >> 2) * 16; c0 < t.n_mma && alive; c0 += 64) {
-                // the three term columns of 16 tokens in flight together, one wait
+            auto hand_back = [&]() {
+                // this thread's last read of the accumulator and of the token tables is done
+                tc05_fence_before_sync();
+                asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(&bar_acc_free)) : "memory");
+            };
+            // the three term columns of 16 tokens in flight together, one wait; summed in term order
+            auto load_sum = [&](uint32_t col, float (&v)[16]) {
                 uint32_t p0[16], p1[16], p2[16];
-                float g[16], u[16];
-                tc05_ld16_issue(trow + c0, p0);
-                tc05_ld16_issue(trow + t.n_mma + c0, p1);
-                tc05_ld16_issue(trow + t.term_row2 + c0, p2);
+                tc05_ld16_issue(trow + col, p0);
+                tc05_ld16_issue(trow + t.n_mma + col, p1);
+                tc05_ld16_issue(trow + t.term_row2 + col, p2);
                 tc05_wait_ld();
 #pragma unroll
                 for (int i = 0; i < 16; ++i)
-                    g[i] = (__uint_as_float(p0[i]) + __uint_as_float(p1[i])) + __uint_as_float(p2[i]);
-                if (MODE == 0) {
-                    tc05_ld16_issue(trow + L::kAccStride + c0, p0);
-                    tc05_ld16_issue(trow + L::kAccStride + t.n_mma + c0, p1);
-                    tc05_ld16_issue(trow + L::kAccStride + t.term_row2 + c0, p2);
-                    tc05_wait_ld();
+                    v[i] = (__uint_as_float(p0[i]) + __uint_as_float(p1[i])) + __uint_as_float(p2[i]);
+            };
+            const int ca = (warp >> 2) * 16, cb = ca + 64;       // this warp's token chunks (TOK <= 128: at most two)
+            const bool has_a = ca < t.n_mma && alive, has_b = cb < t.n_mma && alive;
+            if (MODE == 0) {
+                float g[16], u[16];
+                if (has_a) { load_sum(ca, g); load_sum(L::kAccStride + ca, u); }
+                hand_back();
+                if (has_a) {
 #pragma unroll
                     for (int i = 0; i < 16; ++i)
-                        u[i] = (__uint_as_float(p0[i]) + __uint_as_float(p1[i])) + __uint_as_float(p2[i]);
-                } else {
+                        if (ca + i < t.n_valid)
+                            a.mid[(size_t)(t.slot0 + ca + i) * a.rows + t.m0 + r] = (g[i] / (1.0f + __expf(-g[i]))) * u[i];
+                }
+            } else {
+                float ga[16], gb[16];
+                if (has_a) {
+                    load_sum(ca, ga);
 #pragma unroll
-                    for (int i = 0; i < 16; ++i) u[i] = c0 + i < t.n_valid ? w_of[c0 + i] : 0.f;
+                    for (int i = 0; i < 16; ++i) ga[i] *= ca + i < t.n_valid ? w_of[ca + i] : 0.f;
                 }
-                if (c0 + 64 >= t.n_mma) {
-                    // this thread's last read of the accumulator and of the token tables: hand both back to the
-                    // MMA warp before the stores
-                    tc05_fence_before_sync();
-                    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(&bar_acc_free)) : "memory");
-                    handed_back = true;
-                }
+                if (has_b) {
+                    load_sum(cb, gb);
 #pragma unroll
-                for (int i = 0; i < 16; ++i) {
-                    const int n = c0 + i;
-                    if (n < t.n_valid) {
-                        if (MODE == 0)
-                            a.mid[(size_t)(t.slot0 + n) * a.rows + t.m0 + r] = (g[i] / (1.0f + __expf(-g[i]))) * u[i];
-                        else
-                            a.y[(size_t)(t.slot0 + n) * a.rows + t.m0 + r] = g[i] * u[i];
-                    }
+                    for (int i = 0; i < 16; ++i) gb[i] *= cb + i < t.n_valid ? w_of[cb + i] : 0.f;
                 }
-            }
-            if (!handed_back) {
-                tc05_fence_before_sync();
-                asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(&bar_acc_free)) : "memory");
+                hand_back();
+                if (has_a) {
+#pragma unroll
+                    for (int i = 0; i < 16; ++i)
+                        if (ca + i < t.n_valid) a.y[(size_t)(t.slot0 + ca + i) * a.rows + t.m0 + r] = ga[i];
+                }
+                if (has_b) {
+#pragma unroll
+                    for (int i = 0; i < 16; ++i)
+                        if (cb + i < t.n_valid) a.y[(size_t)(t.slot0 + cb + i) * a.rows + t.m0 + r] = gb[i];
+                }
             }
         };
 

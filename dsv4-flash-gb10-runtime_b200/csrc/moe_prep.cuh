@@ -81,16 +81,51 @@ __global__ void __launch_bounds__(1024) moe_group_kernel(const int* __restrict__
         }
     }
     __syncthreads();
-    if (threadIdx.x == 0) {
-        int off = 0, tu = 0, td = 0;
-        for (int e = 0; e < n_experts; ++e) {
-            g.offsets[e] = off; g.tiles_up[e] = tu; g.tiles_down[e] = td;
-            cursor[e] = off;
-            off += count[e];
-            tu += ((count[e] + tok_up - 1) / tok_up) * (rows_up / kMoeTileRows);
-            td += ((count[e] + tok_down - 1) / tok_down) * (rows_down / kMoeTileRows);
+    // exclusive prefix sums over the experts (thread e owns expert e; blockDim.x == kMoeMaxExperts): pair counts,
+    // gate/up tiles and down tiles, scanned together
+    {
+        __shared__ int warp_sums[3][32];
+        const int e = threadIdx.x, lane = e & 31, wid = e >> 5;
+        const int c = e < n_experts ? count[e] : 0;
+        int v[3] = {c, ((c + tok_up - 1) / tok_up) * (rows_up / kMoeTileRows),
+                    ((c + tok_down - 1) / tok_down) * (rows_down / kMoeTileRows)};
+        int inc[3];
+#pragma unroll
+        for (int q = 0; q < 3; ++q) {
+            int x = v[q];
+#pragma unroll
+            for (int off = 1; off < 32; off <<= 1) {
+                const int y = __shfl_up_sync(kFullMask, x, off);
+                if (lane >= off) x += y;
+            }
+            inc[q] = x;
+            if (lane == 31) warp_sums[q][wid] = x;
         }
-        g.offsets[n_experts] = off; g.tiles_up[n_experts] = tu; g.tiles_down[n_experts] = td;
+        __syncthreads();
+        if (wid == 0) {
+#pragma unroll
+            for (int q = 0; q < 3; ++q) {
+                int x = warp_sums[q][lane];
+#pragma unroll
+                for (int off = 1; off < 32; off <<= 1) {
+                    const int y = __shfl_up_sync(kFullMask, x, off);
+                    if (lane >= off) x += y;
+                }
+                warp_sums[q][lane] = x;                  // inclusive over warps
+            }
+        }
+        __syncthreads();
+        int exc[3];
+#pragma unroll
+        for (int q = 0; q < 3; ++q) exc[q] = inc[q] - v[q] + (wid > 0 ? warp_sums[q][wid - 1] : 0);
+        if (e < n_experts) {
+            g.offsets[e] = exc[0]; g.tiles_up[e] = exc[1]; g.tiles_down[e] = exc[2];
+            cursor[e] = exc[0];
+        }
+        if (e == n_experts - 1) {
+            g.offsets[n_experts] = exc[0] + v[0]; g.tiles_up[n_experts] = exc[1] + v[1];
+            g.tiles_down[n_experts] = exc[2] + v[2];
+        }
     }
     __syncthreads();
     for (int p0 = threadIdx.x; p0 < n_pairs; p0 += blockDim.x * kBatch) {
