@@ -29,10 +29,9 @@ if ROOT not in sys.path:
 N_EXPERTS, TOP_K, HIDDEN, EXPERT_FF = 256, 6, 4096, 2048
 BYTES_PER_EXPERT = 2 * (EXPERT_FF * HIDDEN // 2 + EXPERT_FF * HIDDEN // 32) + (HIDDEN * EXPERT_FF // 2 + HIDDEN * EXPERT_FF // 32)
 LAYER_BYTES = TOP_K * BYTES_PER_EXPERT + 2 * HIDDEN * 2                 # weights + x + out = 80 232 448
-GATE_BYTES = TOP_K * 2 * (EXPERT_FF * HIDDEN // 2 + EXPERT_FF * HIDDEN // 32) + HIDDEN * 2 + TOP_K * EXPERT_FF * 4
-# dram__bytes_read.sum + dram__bytes_write.sum of one gate_up_ring_kernel<4096> launch at this shape
-# (taken from an ncu capture of that launch on a 24-expert bank)
-GATE_DRAM_TRAFFIC = 53_583_000
+# dram__bytes_read.sum + dram__bytes_write.sum of one moe_decode_fused_kernel<4096, 2048> launch at this shape
+# (from an ncu capture of that launch on a 64-expert bank: profiles/moe_decode_fused_kernel_decode_batch1.md)
+FUSED_DRAM_TRAFFIC = 82_390_000
 METRIC = "mxfp4_routed_moe_decode_hbm_throughput"
 UNIT = "GB/s"
 SEED = 1236                                                             # 1234 + index of the configuration
@@ -45,6 +44,14 @@ def measured_hbm_peak():
             return float(json.load(f)["hbm_gbs"]), "measured (MEASURED_PEAKS.json hbm_gbs)"
     except Exception:
         return 6650.0, "fallback (6.65 TB/s, earlier measurement on this pool)"
+
+
+def measured_bf16_peak():
+    try:
+        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
+            return float(json.load(f)["bf16_tflops"])
+    except Exception:
+        return 1590.0
 
 
 # --------------------------------------------------------------------------------------------- clocks
@@ -178,7 +185,7 @@ def workload_config(n_gpus: int):
         "bytes_per_step": LAYER_BYTES,
         "l2": "each step picks 6 experts that the previous 8 steps did not use; the bank is 3.42 GB (L2 is 126 MB)",
         "parallelism": "1 GPU" if n_gpus == 1 else f"{n_gpus} replicas (one token and one bank per GPU, no exchange)",
-        "launch": "CUDA graph of up to 500 steps, replayed",
+        "launch": "CUDA graph of up to 500 steps, replayed (--no-graph: direct launches)",
     }
 
 
@@ -260,12 +267,39 @@ def batched_configs(rt, qz, torch, dist, bank, dev, rank, world):
         flops = T * TOP_K * 2 * 3 * HIDDEN * EXPERT_FF
         min_bytes = distinct * BYTES_PER_EXPERT + 2 * T * HIDDEN * 2
         out[name] = {"tokens": T, "n_gpus": world, "scaling": "strong", "ms": ms, "tflops": flops / ms / 1e9,
+                     "frac_of_measured_bf16_peak": flops / ms / 1e9 / world / measured_bf16_peak(),
+                     "frac_of_measured_hbm_peak": min_bytes / ms / 1e6 / world / measured_hbm_peak()[0],
                      "gbs_min_bytes": min_bytes / ms / 1e6, "distinct_experts": distinct,
                      "max_abs_vs_1gpu_over_inf_norm": parity,
                      "exchange": "none" if world == 1 else "torch.distributed all_to_all_single (NCCL): rows out, rows back"}
     if rt.moe_device_status() != 0:
         raise RuntimeError("a batched kernel gave up on a bounded wait")
     return out
+
+
+def batched_small(rt, torch, bank, dev, T, steps, warmup):
+    """A small case of the batched layer for profiler captures: T tokens, uniform routing over the given bank."""
+    E = bank["w1p"].shape[0]
+    g = torch.Generator().manual_seed(SEED + 3)
+    ids = torch.rand(T, E, generator=g).topk(TOP_K).indices.to(torch.int32).to(dev)
+    w = torch.softmax(torch.randn(T, TOP_K, generator=g), -1).float().to(dev)
+    x = torch.randn(T, HIDDEN, generator=g).to(torch.bfloat16).to(dev)
+    ws = torch.empty(rt.forward_workspace_bytes(T, TOP_K, HIDDEN, EXPERT_FF, HIDDEN, E), dtype=torch.uint8, device=dev)
+    out = torch.empty(T, HIDDEN, dtype=torch.bfloat16, device=dev)
+    for _ in range(warmup):
+        rt.moe_forward(bank, x, ids, w, out=out, workspace=ws)
+    torch.cuda.synchronize()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
+    for _ in range(steps):
+        rt.moe_forward(bank, x, ids, w, out=out, workspace=ws)
+    b.record()
+    torch.cuda.synchronize()
+    ms = a.elapsed_time(b) / steps
+    if rt.moe_device_status() != 0:
+        raise RuntimeError("a batched kernel gave up on a bounded wait")
+    print(json.dumps({"workload": f"batched layer, {T} tokens, uniform routing, {E}-expert bank", "ms": ms,
+                      "tflops": T * TOP_K * 2 * 3 * HIDDEN * EXPERT_FF / ms / 1e9}), flush=True)
 
 
 def run_gpu(args, rank: int, world: int, local_rank: int):
@@ -287,11 +321,12 @@ def run_gpu(args, rank: int, world: int, local_rank: int):
     gen = torch.Generator(device=dev).manual_seed(SEED + rank)
     n_experts = args.experts
     bank = qz.make_expert_bank(n_experts, HIDDEN, EXPERT_FF, dev, seed=SEED + rank, chunk=16)
+    if args.batched_tokens > 0:
+        batched_small(rt, torch, bank, dev, args.batched_tokens, max(1, min(args.steps, 20)), max(args.warmup, 1))
+        return
     x = torch.randn(HIDDEN, generator=gen, device=dev).to(torch.bfloat16)
     graph_steps = max(1, min(args.steps, 500))
     logits = make_logits(graph_steps, dev, gen, n_experts)
-    ids = torch.empty(graph_steps, TOP_K, dtype=torch.int32, device=dev)
-    wts = torch.empty(graph_steps, TOP_K, dtype=torch.float32, device=dev)
     out = torch.empty(HIDDEN, dtype=torch.bfloat16, device=dev)
     ws = torch.empty(gb.decode_workspace_bytes(TOP_K, EXPERT_FF, HIDDEN), dtype=torch.uint8, device=dev)
 
@@ -299,9 +334,8 @@ def run_gpu(args, rank: int, world: int, local_rank: int):
         # router + FFN in one call: the router runs inside the first of the two kernels
         gb.moe_decode_layer(bank, logits[i], x, k=TOP_K, score_func="softmax", out=out, workspace=ws, check=False)
 
-    # one checked call, then capture; the picks of every step are needed to time the first kernel alone
+    # one checked call, then capture
     gb.moe_decode_layer(bank, logits[0], x, k=TOP_K, score_func="softmax", out=out, workspace=ws)
-    rt.moe_route_topk(logits, k=TOP_K, score_func="softmax", ids_out=ids, w_out=wts)
     stream = torch.cuda.Stream(device=dev)
     with torch.cuda.stream(stream):
         for i in range(min(3, graph_steps)):
@@ -311,18 +345,13 @@ def run_gpu(args, rank: int, world: int, local_rank: int):
         with torch.cuda.graph(graph, stream=stream):
             for i in range(graph_steps):
                 layer(i)
-        # a second graph with only the gate/up kernel, to time the dominant kernel alone
-        gate_graph = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(gate_graph, stream=stream):
-            for i in range(graph_steps):
-                gb.mxfp4_grouped_gemv_ids(bank, ids[i], x, wts[i], out=out, workspace=ws, stage_mask=1, check=False)
 
         def run_steps(n):
-            full, rest = divmod(n, graph_steps)
+            full, rest = divmod(n, graph_steps) if not args.no_graph else (0, n)
             for _ in range(full):
                 graph.replay()
             for i in range(rest):
-                layer(i)
+                layer(i % graph_steps)
 
         sampler = ClockSampler(local_rank)
         run_steps(max(args.warmup, 3))
@@ -347,18 +376,6 @@ def run_gpu(args, rank: int, world: int, local_rank: int):
             stream.synchronize()
         clocks = sampler.stop()
         clocks["sampled"] = "timed region" if elapsed_ms > 200 else "timed region + the same load held for <= 1.5 s"
-
-        # dominant kernel alone (gate/up + SwiGLU), CUDA events on its stream
-        gate_graph.replay()
-        stream.synchronize()
-        g0, g1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        reps = max(1, min(20, 4000 // graph_steps))
-        g0.record(stream)
-        for _ in range(reps):
-            gate_graph.replay()
-        g1.record(stream)
-        stream.synchronize()
-        gate_us = g0.elapsed_time(g1) * 1e3 / (reps * graph_steps)
 
         # end to end through the binding with HOST buffers: pinned x and logits in, bf16 out back, every step
         e2e_steps = max(1, min(args.steps, 200))
@@ -399,9 +416,9 @@ def run_gpu(args, rank: int, world: int, local_rank: int):
         batched = batched_configs(rt, qz, torch, dist, bank, dev, rank, world)
 
     if world > 1:
-        t = torch.tensor([elapsed_ms, e2e_ms, gate_us], device=dev, dtype=torch.float64)
+        t = torch.tensor([elapsed_ms, e2e_ms], device=dev, dtype=torch.float64)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        elapsed_ms, e2e_ms, gate_us = (float(v) for v in t.tolist())
+        elapsed_ms, e2e_ms = (float(v) for v in t.tolist())
     if rank != 0:
         if world > 1:
             dist.destroy_process_group()
@@ -410,7 +427,10 @@ def run_gpu(args, rank: int, world: int, local_rank: int):
     peak, peak_src = measured_hbm_peak()
     value = world * args.steps * LAYER_BYTES / (elapsed_ms * 1e-3) / 1e9
     e2e_value = world * e2e_steps * LAYER_BYTES / (e2e_ms * 1e-3) / 1e9
-    gate_gbs = GATE_BYTES / (gate_us * 1e-6) / 1e9
+    # a step is ONE launch of the fused kernel, so the kernel's average launch duration is the timed region / steps
+    # (CUDA events on the launching stream; the gaps between launches count against the kernel)
+    launch_us = elapsed_ms / args.steps * 1e3
+    kernel_gbs = LAYER_BYTES / (launch_us * 1e-6) / 1e9
     line = {
         "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": elapsed_ms / args.steps, "us_per_layer": elapsed_ms / args.steps * 1e3,
@@ -423,9 +443,9 @@ def run_gpu(args, rank: int, world: int, local_rank: int):
                 "what": "pinned host x + logits -> device, router, FFN, bf16 out -> pinned host, stream synchronise; every step"},
         "gpu_launches": args.steps,
         "kernels_per_step": "1 x moe_decode_fused_kernel<4096,2048> (router + gate/up + grid barrier + down)",
-        "roofline": {"bound": "hbm", "kernel": "gate_up_ring_kernel<4096> (W1/W3 + SwiGLU, 67 % of the layer's bytes)",
-                     "achieved": gate_gbs, "peak": peak, "unit": "GB/s", "frac": gate_gbs / peak,
-                     "traffic": GATE_DRAM_TRAFFIC, "algorithmic_bytes": GATE_BYTES, "us_per_launch": gate_us,
+        "roofline": {"bound": "hbm", "kernel": "moe_decode_fused_kernel<4096, 2048> (the step's only kernel)",
+                     "achieved": kernel_gbs, "peak": peak, "unit": "GB/s", "frac": kernel_gbs / peak,
+                     "traffic": FUSED_DRAM_TRAFFIC, "algorithmic_bytes": LAYER_BYTES, "us_per_launch": launch_us,
                      "peak_source": peak_src},
         "clocks": clocks,
     }
@@ -465,6 +485,9 @@ def main():
     ap.add_argument("--warmup", type=int, default=1000)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-batched", action="store_true", help="skip the batched / expert-parallel side measurements")
+    ap.add_argument("--no-graph", action="store_true", help="launch every step directly (profiler captures)")
+    ap.add_argument("--batched-tokens", type=int, default=0,
+                    help="profiler captures: run only the batched layer on this many tokens (uniform routing) and exit")
     ap.add_argument("--experts", type=int, default=N_EXPERTS,
                     help="experts in the resident bank; smaller banks (>= 24) are for profiler captures only")
     args = ap.parse_args()
