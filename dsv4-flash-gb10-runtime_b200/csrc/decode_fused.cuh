@@ -4,16 +4,16 @@
 // the drain between the kernels and the second set-up: while a CTA waits at the grid barrier for the other CTAs'
 // SwiGLU rows, its copies of the first W2 rows are already in flight.
 //
-// Launched cooperatively with one CTA per SM (the runtime guarantees that all CTAs are resident, which is what
-// makes the grid barrier legal); the barrier itself is cooperative_groups::grid_group::sync().
+// Launched with one CTA per SM, either cooperatively (the runtime guarantees that all CTAs are resident, which is
+// what makes a grid barrier legal) or with programmatic stream serialisation (the next layer's CTAs start as this
+// layer's exit; legal as long as no second grid of this kernel is in flight on the device).  The barrier is a
+// bounded sense-reversing one, split into arrive and wait.
 //
 // 16 warps per CTA.  Each warp owns a private 8.5 KB ring: two slots of one (W1 row, W3 row, 2 scale rows) pair in
 // the first phase, four slots of two (W2 row, scale row) in the second.  Second-phase work is cut into
 // (expert, 2-row chunk) tasks dealt round-robin to the warps; a warp reloads the expert's fp16 intermediate from
 // shared memory into registers at the start of every task (8 x 128-bit loads against ~200 arithmetic instructions).
 #pragma once
-
-#include <cooperative_groups.h>
 
 #include "grouped_ring.cuh"
 
@@ -23,6 +23,45 @@ constexpr int kFusedWarps = 16;
 constexpr int kFusedStagesA = 2;
 constexpr int kFusedRowsB = 2;
 constexpr int kFusedCap = 64;          // output rows per CTA
+
+// Grid barrier of the fused kernel, split into ARRIVE and WAIT so that a CTA can queue its next weight copies in
+// between.  Every warp arrives on its own with a fire-and-forget release increment of a counter that only grows;
+// one lane per CTA waits until the counter has moved `arrivals` past the base it had when the grid started.  The
+// base is kept in device memory and advanced by the last CTA to leave the kernel, off the critical path (the next
+// grid reads it only after this one has completed).  Critical chain: the last warp's release increment, then one
+// poll - no reset and no generation word in between.
+// All CTAs of the grid must become resident without waiting for this grid to finish: one CTA per SM, and no other
+// grid of this kernel in flight on the device (the cooperative launch guarantees it; the programmatic launch relies
+// on the caller).  Bounded: a CTA that gives up records status 3 and carries on (its results are then garbage, the
+// status says so; dsv4_b200_device_status() then also resets the three words).
+__device__ unsigned int g_fused_count = 0;       // arrivals, monotonic
+__device__ unsigned int g_fused_base = 0;        // value of g_fused_count before the grid in flight
+__device__ unsigned int g_fused_exits = 0;       // CTAs of the grid in flight that have left
+
+// The lane of a warp that made the warp's global writes: the release orders them before the increment.
+__device__ __forceinline__ void fused_barrier_arrive() {
+    asm volatile("red.release.gpu.global.add.u32 [%0], 1;" ::"l"(&g_fused_count) : "memory");
+}
+
+// One lane per CTA; `base` was read from g_fused_base at the start of the kernel.
+__device__ __forceinline__ bool fused_barrier_wait(unsigned int base, unsigned int arrivals) {
+    for (uint32_t it = 0; it < kSpinLimit; ++it) {
+        unsigned int now;
+        asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(now) : "l"(&g_fused_count) : "memory");
+        if (now - base >= arrivals) return true;
+        if (it > 256) __nanosleep(32);
+    }
+    atomicExch(&g_device_status, 3);
+    return false;
+}
+
+// One thread per CTA at the end of the kernel: the last CTA to leave moves the base past this grid's arrivals.
+__device__ __forceinline__ void fused_barrier_leave(unsigned int base, unsigned int arrivals) {
+    if (atomicAdd(&g_fused_exits, 1u) == gridDim.x - 1) {
+        g_fused_exits = 0;
+        g_fused_base = base + arrivals;
+    }
+}
 
 template <int KT, int HT>
 struct FusedLayout {
@@ -113,6 +152,9 @@ __global__ void __launch_bounds__(kFusedWarps * 32, 1) moe_decode_fused_kernel(c
     };
 
     pdl_wait();
+    // (the previous grid of this kernel, if any, has completed: its last CTA has advanced the base)
+    unsigned int barrier_base = 0;
+    if (lane == 0) asm volatile("ld.relaxed.gpu.global.u32 %0, [%1];" : "=r"(barrier_base) : "l"(&g_fused_base) : "memory");
     if (routed) {
         if (warp == 0) {
             int id;
@@ -188,19 +230,26 @@ __global__ void __launch_bounds__(kFusedWarps * 32, 1) moe_decode_fused_kernel(c
             }
         }
     }
+    // ------------------------------------------------------------------ grid barrier, first half
+    // Every warp arrives on its own as soon as its SwiGLU rows are written (lane 0 wrote them); the W2 copies are
+    // queued after that, and the wait for the other warps of the grid comes last.
+    __shared__ int barrier_ok;
+    const bool arbiter = threadIdx.x == (NW - 1) * 32;
+    if (lane == 0) fused_barrier_arrive();
+    __syncwarp();
     // ------------------------------------------------------------------ phase B set-up: request W2 rows, then wait
     const int o_begin = (int)((long long)a.O * blockIdx.x / gridDim.x);
     const int o_end = (int)((long long)a.O * (blockIdx.x + 1) / gridDim.x);
     const int n_local = o_end - o_begin;
     const int n_chunks = (n_local + R - 1) / R;
-    const int n_tasks = a.E * n_chunks;                              // task t: expert t % E, chunk t / E
-    const uint32_t inv_e = (65536u + a.E - 1) / a.E;                 // t / E == (t * inv_e) >> 16 for t < 4096, E <= 8
+    const int n_tasks = a.E * n_chunks;                              // task t: expert t / n_chunks, chunk t % n_chunks
+    // t / n_chunks == (t * inv_c) >> 16: exact for t < 256 and n_chunks <= 32 (E <= 8, at most 64 rows per CTA)
+    const uint32_t inv_c = (65536u + n_chunks - 1) / n_chunks;
 
     auto issue_b = [&](int t, int s) {
         if (lane < 2) {
-            const int c = (int)(((uint32_t)t * inv_e) >> 16);
-            const int e = t - c * a.E;
-            const int l0 = c * R;
+            const int e = (int)(((uint32_t)t * inv_c) >> 16);
+            const int l0 = (t - e * n_chunks) * R;
             const long long eid = (long long)expert_of_slot[e];
             const uint32_t rows = (uint32_t)min(R, n_local - l0);
             const bool scale = lane == 1;
@@ -213,15 +262,18 @@ __global__ void __launch_bounds__(kFusedWarps * 32, 1) moe_decode_fused_kernel(c
             bulk_copy_g2s(dst, src, rows * rb, bar);
         }
     };
+    // Only the first slot of every warp is requested before the barrier: loads issued behind a full ring of queued
+    // copies (the barrier's polls, the intermediate) would wait for all of them, and the arithmetic of this phase
+    // could not start before the whole ring had arrived.  The other slots follow once the loads of the
+    // intermediate are in flight.
     int tb[SB];
-#pragma unroll
-    for (int s = 0; s < SB; ++s) {
-        tb[s] = claim(&next_task);
-        if (tb[s] < n_tasks && alive) issue_b(tb[s], s);
-    }
+    tb[0] = claim(&next_task);
+    if (tb[0] < n_tasks && alive) issue_b(tb[0], 0);
 
-    __threadfence();
-    cooperative_groups::this_grid().sync();                          // every SwiGLU row of every expert is written
+    // grid barrier, second half: every SwiGLU row of every expert is written
+    if (arbiter) barrier_ok = fused_barrier_wait(barrier_base, gridDim.x * NW) ? 1 : 0;
+    __syncthreads();
+    if (!barrier_ok) alive = false;
 
     // intermediates -> fp16, one scale per expert, once per CTA
     {
@@ -236,6 +288,14 @@ __global__ void __launch_bounds__(kFusedWarps * 32, 1) moe_decode_fused_kernel(c
 #pragma unroll
             for (int i = 0; i < 8; ++i) v[p][i] = 0.f;
             if (idx8 < n8) load8_as_float(a.mid + (size_t)idx8 * 8, v[p]);
+        }
+#pragma unroll
+        for (int s = 1; s < SB; ++s) {                               // the rest of the ring
+            tb[s] = claim(&next_task);
+            if (tb[s] < n_tasks && alive) issue_b(tb[s], s);
+        }
+#pragma unroll
+        for (int p = 0; p < kPieces; ++p) {
             uint32_t m = amax_bits8(v[p]);
 #pragma unroll
             for (int off = 16; off > 0; off >>= 1) m = max(m, __shfl_xor_sync(kFullMask, m, off));
@@ -263,6 +323,10 @@ __global__ void __launch_bounds__(kFusedWarps * 32, 1) moe_decode_fused_kernel(c
         const uint32_t lane_w = ring + lane * 16;
         const uint32_t lane_s = ring + R * L::kRowPB + lane;
         uint32_t parity = 0;
+        // tasks are numbered expert-major, so a warp reloads its blocks of the intermediate only when it crosses
+        // into another expert
+        __half2 m2[L::kBplB][16];
+        int cur_e = -1;
         for (bool any = true; any; parity ^= 1) {
             any = false;
 #pragma unroll
@@ -270,11 +334,9 @@ __global__ void __launch_bounds__(kFusedWarps * 32, 1) moe_decode_fused_kernel(c
                 const int t = tb[s];
                 if (t < n_tasks && alive) {
                     any = true;
-                    const int c = (int)(((uint32_t)t * inv_e) >> 16);
-                    const int e = t - c * a.E;
-                    const int l0 = c * R;
-                    __half2 m2[L::kBplB][16];
-                    lane_blocks_from_smem<L::kBplB>(vec + (size_t)e * HT, lane, m2);
+                    const int e = (int)(((uint32_t)t * inv_c) >> 16);
+                    const int l0 = (t - e * n_chunks) * R;
+                    if (e != cur_e) { lane_blocks_from_smem<L::kBplB>(vec + (size_t)e * HT, lane, m2); cur_e = e; }
                     alive = mbar_wait_bounded(bars_b + 8 * s, parity, 2);
                     float v[R];
 #pragma unroll
@@ -306,6 +368,7 @@ __global__ void __launch_bounds__(kFusedWarps * 32, 1) moe_decode_fused_kernel(c
         for (int k = 0; k < a.E; ++k) acc = fmaf(weight_of_slot[k], part[t][k], acc);
         a.out[o_begin + t] = __float2bfloat16(acc);
     }
+    if (threadIdx.x == (NW - 1) * 32) fused_barrier_leave(barrier_base, gridDim.x * NW);
 }
 
 }  // namespace dsv4

@@ -352,14 +352,17 @@ static cudaError_t allow_smem(Kernel kernel, size_t bytes, int (&done)[64]) {
     return err;
 }
 
-static bool fused_enabled() {
+// DSV4_B200_FUSED: "0" two chained kernels; "pdl" the single kernel launched with programmatic stream
+// serialisation and its own grid barrier; anything else the single kernel launched cooperatively.
+static int fused_mode() {
     static int v = -1;
     if (v < 0) {
         const char* e = std::getenv("DSV4_B200_FUSED");
-        v = (e && e[0] == '0') ? 0 : 1;
+        v = (e && e[0] == '0') ? 0 : ((e && e[0] == 'p') ? 2 : 1);
     }
-    return v == 1;
+    return v;
 }
+static bool fused_enabled() { return fused_mode() != 0; }
 
 // Single persistent kernel (decode_fused.cuh), launched cooperatively with one CTA per SM.
 // Returns 1 when it cannot be used here (the caller then launches the two chained kernels).
@@ -394,13 +397,18 @@ static int grouped_launch_fused(const GroupedArgs& a, cudaStream_t stream, int h
     cfg.blockDim = dim3(kFusedWarps * 32);
     cfg.dynamicSmemBytes = L::kBytes;
     cfg.stream = stream;
-    cudaLaunchAttribute attr[2];
-    attr[0].id = cudaLaunchAttributeCooperative;
-    attr[0].val.cooperative = 1;
-    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    attr[1].val.programmaticStreamSerializationAllowed = 1;
+    // a cooperative launch is not combined with programmatic stream serialisation: one or the other
+    const bool own_barrier = fused_mode() == 2;      // (launch attribute only: the kernel is the same)
+    cudaLaunchAttribute attr[1];
+    if (own_barrier) {
+        attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[0].val.programmaticStreamSerializationAllowed = 1;
+    } else {
+        attr[0].id = cudaLaunchAttributeCooperative;
+        attr[0].val.cooperative = 1;
+    }
     cfg.attrs = attr;
-    cfg.numAttrs = 1;        // a cooperative launch is not combined with programmatic stream serialisation
+    cfg.numAttrs = 1;
     const cudaError_t err = cudaLaunchKernelEx(&cfg, kernel, a, h_shift, rt);
     if (err != cudaSuccess) {
         cudaGetLastError();
@@ -742,7 +750,13 @@ DSV4_API int mxfp4_dequant_bf16(const uint8_t* packed, const uint8_t* scale, lon
 DSV4_API int dsv4_b200_device_status(void) {
     int v = 0, zero = 0;
     if (cudaMemcpyFromSymbol(&v, g_device_status, sizeof(int)) != cudaSuccess) return -1;
-    if (v != 0) cudaMemcpyToSymbol(g_device_status, &zero, sizeof(int));
+    if (v != 0) {
+        cudaMemcpyToSymbol(g_device_status, &zero, sizeof(int));
+        // a grid barrier that gave up leaves its words out of step: start again from zero
+        cudaMemcpyToSymbol(g_fused_count, &zero, sizeof(int));
+        cudaMemcpyToSymbol(g_fused_base, &zero, sizeof(int));
+        cudaMemcpyToSymbol(g_fused_exits, &zero, sizeof(int));
+    }
     return v;
 }
 

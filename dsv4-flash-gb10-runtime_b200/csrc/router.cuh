@@ -45,27 +45,34 @@ __device__ __forceinline__ void route_token(const float* __restrict__ row, int n
                 s[i] = sqrtf(fmaxf(g, 0.0f) + log1pf(expf(-fabsf(g))));
             }
     }
+    // Top-k by k rounds of warp-wide arg-max on order-preserving integer keys (redux.sync): largest score, lowest
+    // expert index on ties; NaN scores are never picked.
+    uint32_t key[PL];
+#pragma unroll
+    for (int i = 0; i < PL; ++i) {
+        const uint32_t bits = __float_as_uint(s[i]);
+        key[i] = (s[i] != s[i] || s[i] == -INFINITY) ? 0u : (bits ^ ((bits >> 31) ? 0xffffffffu : 0x80000000u));
+    }
     float my_score = 0.f, sum = 0.f;
     id = -1;
     for (int j = 0; j < k; ++j) {
-        float best = -INFINITY;
-        int best_idx = 0x7fffffff;
+        uint32_t best = 0;
+        int best_i = 0;
 #pragma unroll
         for (int i = 0; i < PL; ++i)
-            if (s[i] > best) { best = s[i]; best_idx = i * 32 + lane; }   // strict: lowest index wins in a lane
-#pragma unroll
-        for (int off = 16; off > 0; off >>= 1) {
-            const float ob = __shfl_xor_sync(kFullMask, best, off);
-            const int oi = __shfl_xor_sync(kFullMask, best_idx, off);
-            if (ob > best || (ob == best && oi < best_idx)) { best = ob; best_idx = oi; }
-        }
-        if (lane == j) { my_score = best; id = best_idx; }
-        if ((best_idx & 31) == lane) {
+            if (key[i] > best) { best = key[i]; best_i = i; }             // strict: lowest index wins in a lane
+        const uint32_t top = __reduce_max_sync(kFullMask, best);
+        const int cand = (best == top && top != 0u) ? best_i * 32 + lane : 0x7fffffff;
+        const int win = __reduce_min_sync(kFullMask, cand);
+        const uint32_t bits = (top >> 31) ? (top ^ 0x80000000u) : ~top;
+        const float best_score = top != 0u ? __uint_as_float(bits) : -INFINITY;
+        if (lane == j) { my_score = best_score; id = win != 0x7fffffff ? win : 0; }
+        if ((win & 31) == lane && win != 0x7fffffff) {
 #pragma unroll
             for (int i = 0; i < PL; ++i)
-                if (i == (best_idx >> 5)) s[i] = -INFINITY;
+                if (i == (win >> 5)) key[i] = 0u;
         }
-        sum += score_func == 0 ? __expf(best - row_max) : best;
+        sum += score_func == 0 ? __expf(best_score - row_max) : best_score;
     }
     w = score_func == 0 ? __expf(my_score - row_max) / sum : my_score / (sum + eps) * scaling;
 }
