@@ -10,9 +10,10 @@
 // bounded sense-reversing one, split into arrive and wait.
 //
 // 16 warps per CTA.  Each warp owns a private 8.5 KB ring: two slots of one (W1 row, W3 row, 2 scale rows) pair in
-// the first phase, four slots of two (W2 row, scale row) in the second.  Second-phase work is cut into
-// (expert, 2-row chunk) tasks dealt round-robin to the warps; a warp reloads the expert's fp16 intermediate from
-// shared memory into registers at the start of every task (8 x 128-bit loads against ~200 arithmetic instructions).
+// the first phase, two slots of four (W2 row, scale row) in the second (4 352 bytes per slot in both: the fixed
+// cost of a task - wait, butterfly reduction, claim, refill - is paid once per 4 KB of weights).  Second-phase work
+// is cut into (expert, 4-row chunk) tasks numbered expert-major and claimed from a shared counter; a warp reloads
+// its blocks of the expert's fp16 intermediate from shared memory only when it crosses into another expert.
 #pragma once
 
 #include "grouped_ring.cuh"
@@ -21,7 +22,7 @@ namespace dsv4 {
 
 constexpr int kFusedWarps = 16;
 constexpr int kFusedStagesA = 2;
-constexpr int kFusedRowsB = 2;
+constexpr int kFusedRowsB = 4;
 constexpr int kFusedCap = 64;          // output rows per CTA
 
 // Grid barrier of the fused kernel, split into ARRIVE and WAIT so that a CTA can queue its next weight copies in
