@@ -84,7 +84,8 @@ DSV4_API size_t mxfp4_moe_forward_workspace_bytes(int n_tokens, int k, int K_in,
 }
 
 // x bf16 [n_tokens, K_in]; bank tensors stacked over n_experts as in mxfp4_grouped_gemv_topk_ids; ids int32
-// [n_tokens, k] (a token lists an expert at most once), weights FP32 [n_tokens, k]; out bf16 [n_tokens, out_dim].
+// [n_tokens, k] (a token lists an expert at most once; a negative id marks a pair to skip, which is how an
+// expert-parallel caller masks the experts of other ranks), weights FP32 [n_tokens, k]; out bf16 [n_tokens, out_dim].
 // Shapes: K_in and hidden multiples of 256, hidden and out_dim multiples of 128, n_experts <= 1024.
 // Returns 0, -1 bad shape, -2 null / misaligned pointer, -3 launch failure.
 static int moe_forward_impl(int path, const __nv_bfloat16* x, const uint8_t* bank_W1_packed, const uint8_t* bank_W3_packed,

@@ -72,12 +72,13 @@ __global__ void __launch_bounds__(1024) moe_group_kernel(const int* __restrict__
 #pragma unroll
         for (int i = 0; i < kBatch; ++i) {
             const int p = p0 + i * blockDim.x;
-            e[i] = p < n_pairs ? __ldg(ids + p) : -2;
+            e[i] = p < n_pairs ? __ldg(ids + p) : -1;
         }
 #pragma unroll
         for (int i = 0; i < kBatch; ++i) {
             if (e[i] >= 0 && e[i] < n_experts) atomicAdd(&count[e[i]], 1);
-            else if (e[i] != -2) atomicExch(status, 3);  // expert id out of range: the pair is dropped
+            else if (e[i] >= n_experts) atomicExch(status, 3);   // id past the bank: dropped and reported
+            // (a negative id marks a pair that is not this bank's: dropped silently, e.g. another rank's expert)
         }
     }
     __syncthreads();
@@ -133,7 +134,7 @@ __global__ void __launch_bounds__(1024) moe_group_kernel(const int* __restrict__
 #pragma unroll
         for (int i = 0; i < kBatch; ++i) {
             const int p = p0 + i * blockDim.x;
-            e[i] = p < n_pairs ? __ldg(ids + p) : -2;
+            e[i] = p < n_pairs ? __ldg(ids + p) : -1;
         }
 #pragma unroll
         for (int i = 0; i < kBatch; ++i) {
@@ -142,7 +143,7 @@ __global__ void __launch_bounds__(1024) moe_group_kernel(const int* __restrict__
                 const int slot = atomicAdd(&cursor[e[i]], 1);
                 g.slot_pair[slot] = p;
                 g.pair_slot[p] = slot;
-            } else if (e[i] != -2) {
+            } else if (p < n_pairs) {
                 g.pair_slot[p] = -1;
             }
         }

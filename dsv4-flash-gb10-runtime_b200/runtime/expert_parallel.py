@@ -2,16 +2,19 @@
 (expert e lives on rank e // (E / world)); tokens are data-parallel.
 
 Per layer and rank:
-  1. every (token, expert) pair is sent to the rank that owns the expert: one all-to-all of the pair counts,
-     one of the activation rows (bf16 [pairs, K]) with their local expert index and router weight;
-  2. the owner runs the batched tensor-core layer (moe_batched.moe_forward) over the rows it received, each row
-     being a one-expert token, and gets one weighted output row per pair;
-  3. the output rows travel back with the mirrored all-to-all;
-  4. every token sums its k rows in the router's order (fixed order: deterministic).
+  1. a token is sent ONCE to every rank that owns at least one of its k experts (at most min(k, world) copies,
+     not k): one all-to-all of the row counts, one of the rows, each row carrying the activation (bf16 [K]), the
+     token's k global expert ids and its k router weights;
+  2. the owner masks the ids that are not its own (negative id = skip) and runs the batched tensor-core layer
+     (moe_batched.moe_forward) over the rows it received: one partial output row per (token, rank), already
+     weighted and summed over that rank's experts;
+  3. the partial rows travel back with the mirrored all-to-all;
+  4. every token adds its partial rows in rank order in FP32 (fixed order: deterministic) and rounds to bf16.
 
 The collectives are torch.distributed all_to_all_single calls (NCCL on GPUs, gloo in the CPU tests); received
-rows land in this rank's own memory before any kernel reads them.  The reference has no multi-GPU path at all;
-the contract is that the result equals the single-GPU layer on the same inputs.
+rows land in this rank's own memory before any kernel reads them.  One host synchronisation per layer (the split
+sizes of the variable all-to-all).  The reference has no multi-GPU path at all; the contract is that the result
+equals the single-GPU layer on the same inputs up to the bf16 rounding of the partial rows.
 """
 from __future__ import annotations
 
@@ -22,18 +25,17 @@ import torch.distributed as dist
 
 
 def plan_dispatch(ids: torch.Tensor, experts_per_rank: int, world: int):
-    """Sort the T*k pairs by destination rank.
+    """Which token goes to which rank.
 
-    Returns (order, send_counts, local_expert): `order` lists pair indices (t * k + j) grouped by destination rank,
-    stable inside a rank; `send_counts[r]` pairs go to rank r; `local_expert` is the expert's index on its owner,
-    in `order`.
+    Returns (token_of, send_counts): `token_of` lists token indices grouped by destination rank (ranks ascending,
+    tokens ascending inside a rank, a token at most once per rank); `send_counts[r]` rows go to rank r.
     """
-    flat = ids.reshape(-1).to(torch.int64)
-    dest = torch.div(flat, experts_per_rank, rounding_mode="floor")
-    order = torch.sort(dest, stable=True).indices
-    send_counts = torch.bincount(dest, minlength=world)[:world]
-    local_expert = (flat - dest * experts_per_rank)[order].to(torch.int32)
-    return order, send_counts, local_expert
+    T = ids.shape[0]
+    dest = torch.div(ids.to(torch.int64), experts_per_rank, rounding_mode="floor")
+    mask = torch.zeros(T, world, dtype=torch.bool, device=ids.device)
+    mask.scatter_(1, dest.clamp_(0, world - 1), True)
+    pairs = mask.t().nonzero()                       # (rank, token), sorted by rank then token
+    return pairs[:, 1].contiguous(), mask.sum(dim=0)
 
 
 def _all_to_all_rows(rows: torch.Tensor, send_counts, recv_counts, group) -> torch.Tensor:
@@ -45,41 +47,53 @@ def _all_to_all_rows(rows: torch.Tensor, send_counts, recv_counts, group) -> tor
 
 def ep_moe_forward(x: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor, n_experts: int,
                    local_forward: Callable[[torch.Tensor, torch.Tensor, torch.Tensor], torch.Tensor],
-                   group: Optional[dist.ProcessGroup] = None) -> torch.Tensor:
+                   group: Optional[dist.ProcessGroup] = None, out_dim: Optional[int] = None) -> torch.Tensor:
     """x [T, K] (this rank's tokens), ids int32 [T, k] GLOBAL expert ids, weights float32 [T, k].
 
-    `local_forward(rows [R, K], local_ids int32 [R, 1], w float32 [R, 1]) -> [R, O]` runs this rank's experts
-    (on a GPU: moe_forward bound to the local bank).  Returns [T, O] in x's dtype.
+    `local_forward(rows [R, K], local_ids int32 [R, k], w float32 [R, k]) -> [R, O]` runs this rank's experts on
+    the rows (on a GPU: moe_forward bound to the local bank); local_ids are indices into the local bank, -1 where
+    the expert belongs to another rank.  `out_dim` is O (default: K).  Returns [T, O] in x's dtype.
     """
     world = dist.get_world_size(group)
+    rank = dist.get_rank(group)
     if n_experts % world:
         raise ValueError(f"{n_experts} experts do not split over {world} ranks")
+    per = n_experts // world
     T, k = ids.shape
-    order, send_counts, local_expert = plan_dispatch(ids, n_experts // world, world)
-    send_counts_l = [int(c) for c in send_counts.tolist()]
+    K = x.shape[1]
+    O = K if out_dim is None else int(out_dim)
+    token_of, send_counts = plan_dispatch(ids, per, world)
+    counts_out = send_counts.to(torch.int64)
     counts_in = torch.empty(world, dtype=torch.int64, device=x.device)
-    dist.all_to_all_single(counts_in, send_counts.to(torch.int64).to(x.device), group=group)
-    recv_counts_l = [int(c) for c in counts_in.tolist()]
+    dist.all_to_all_single(counts_in, counts_out, group=group)
+    both = torch.stack([counts_out, counts_in]).tolist()              # the layer's one host synchronisation
+    send_l, recv_l = [int(c) for c in both[0]], [int(c) for c in both[1]]
 
-    token_of = torch.div(order, k, rounding_mode="floor")
-    rows = _all_to_all_rows(x[token_of], send_counts_l, recv_counts_l, group)
-    loc = _all_to_all_rows(local_expert.to(x.device).unsqueeze(1), send_counts_l, recv_counts_l, group)
-    w_sorted = weights.reshape(-1)[order].unsqueeze(1)
-    wts = _all_to_all_rows(w_sorted, send_counts_l, recv_counts_l, group)
+    # one payload row per (token, destination): activation | k ids | k weights, as bytes
+    xb = x.contiguous().view(torch.uint8).view(T, -1)
+    ib = ids.to(torch.int32).contiguous().view(torch.uint8).view(T, -1)
+    wb = weights.to(torch.float32).contiguous().view(torch.uint8).view(T, -1)
+    payload = torch.cat([xb, ib, wb], dim=1)[token_of]
+    got = _all_to_all_rows(payload, send_l, recv_l, group)
+    nx, ni = xb.shape[1], ib.shape[1]
+    rows = got[:, :nx].contiguous().view(x.dtype).view(-1, K)
+    gids = got[:, nx:nx + ni].contiguous().view(torch.int32).view(-1, k)
+    wts = got[:, nx + ni:].contiguous().view(torch.float32).view(-1, k)
+    local = gids - rank * per
+    local = torch.where((local >= 0) & (local < per), local, torch.full_like(local, -1))
 
     if rows.shape[0] > 0:
-        y = local_forward(rows, loc.contiguous(), wts.contiguous())
+        y = local_forward(rows, local.contiguous(), wts)
     else:
-        y = rows.new_empty((0, 0))
-    out_dim = torch.tensor([y.shape[1] if y.numel() else 0], dtype=torch.int64, device=x.device)
-    dist.all_reduce(out_dim, op=dist.ReduceOp.MAX, group=group)      # a rank without rows learns the width
-    O = int(out_dim.item())
-    if y.numel() == 0:
         y = rows.new_empty((0, O))
-    back = _all_to_all_rows(y, recv_counts_l, send_counts_l, group)   # rows return in `order`
-    per_pair = torch.empty((T * k, O), dtype=back.dtype, device=x.device)
-    per_pair[order] = back
-    return per_pair.view(T, k, O).float().sum(dim=1).to(x.dtype)       # j = 0 .. k-1: fixed order
+    back = _all_to_all_rows(y, recv_l, send_l, group)                 # partial rows return in `token_of` order
+    acc = torch.zeros(T, O, dtype=torch.float32, device=x.device)
+    start = 0
+    for n in send_l:                                                  # rank order; a token at most once per rank
+        if n:
+            acc.index_add_(0, token_of[start:start + n], back[start:start + n].float())
+        start += n
+    return acc.to(x.dtype)
 
 
 def shard_bank(bank: Dict[str, torch.Tensor], rank: int, world: int) -> Dict[str, torch.Tensor]:

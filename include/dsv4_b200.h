@@ -127,8 +127,9 @@ int fp8_e4m3_gemv_m1_f32scale(const uint16_t* x, const uint8_t* W_fp8, const flo
 
 /* Routed-expert MoE layer for a batch of tokens on the tensor cores: out[t] = sum_j weights[t,j] * FFN_{ids[t,j]}(x[t]).
  * x bf16 [n_tokens, K_in]; bank tensors as in mxfp4_grouped_gemv_topk_ids; ids int32 [n_tokens, k]; weights FP32
- * [n_tokens, k]; out bf16 [n_tokens, out_dim].  K_in, hidden multiples of 256; out_dim multiple of 128;
- * n_experts <= 1024.  Returns -1 bad shape, -2 null / misaligned pointer, -3 launch failure. */
+ * [n_tokens, k]; out bf16 [n_tokens, out_dim].  A negative id marks a pair to skip (an expert-parallel caller masks
+ * the experts of other ranks this way); an id >= n_experts is dropped and reported by mxfp4_moe_device_status().
+ * K_in, hidden multiples of 256; out_dim multiple of 128; n_experts <= 1024.  Returns -1 bad shape, -2 null / misaligned pointer, -3 launch failure. */
 int mxfp4_moe_forward(const uint16_t* x, const uint8_t* bank_W1_packed, const uint8_t* bank_W3_packed,
                       const uint8_t* bank_W2_packed, const uint8_t* bank_W1_scale, const uint8_t* bank_W3_scale,
                       const uint8_t* bank_W2_scale, const int* ids, const float* weights, int n_tokens, int n_experts,

@@ -18,7 +18,17 @@ def _free_port():
 
 def _fake_expert(rows, expert_global, w):
     # stands for FFN_e(x) * w: distinguishes experts and keeps the row content
-    return (rows.float() * (expert_global.float() + 1.0) * w).to(rows.dtype)
+    return rows.float() * (expert_global.float() + 1.0) * w
+
+
+def _fake_layer(rows, global_ids, w, lo, hi):
+    """Weighted sum over the experts lo <= id < hi of every row, rounded to the row dtype (what one rank returns)."""
+    acc = torch.zeros(rows.shape[0], rows.shape[1])
+    for j in range(global_ids.shape[1]):
+        e = global_ids[:, j:j + 1]
+        mine = (e >= lo) & (e < hi)
+        acc += torch.where(mine, _fake_expert(rows, e, w[:, j:j + 1]), torch.zeros(()))
+    return acc.to(rows.dtype)
 
 
 def _worker(rank, world, port, T, E, k, K):
@@ -37,12 +47,16 @@ def _worker(rank, world, port, T, E, k, K):
     per = E // world
 
     def local_forward(rows, local_ids, wts):
-        return _fake_expert(rows, local_ids + rank * per, wts)
+        assert local_ids.shape == (rows.shape[0], k) and int(local_ids.max()) < per and int(local_ids.min()) >= -1
+        assert bool((local_ids >= 0).any(dim=1).all())                # no row was sent to a rank that owns none of its experts
+        gids = torch.where(local_ids >= 0, local_ids + rank * per, torch.full_like(local_ids, -1))
+        return _fake_layer(rows, gids, wts, rank * per, (rank + 1) * per)
 
     out = ep.ep_moe_forward(x, ids, w, E, local_forward)
+    # the same arithmetic in one process: partial row per owner rank (rounded), added in rank order in FP32
     want = torch.zeros(T, K)
-    for j in range(k):
-        want += _fake_expert(x, ids[:, j:j + 1], w[:, j:j + 1]).float()
+    for r in range(world):
+        want += _fake_layer(x, ids, w, r * per, (r + 1) * per).float()
     ok = torch.equal(out, want.to(torch.bfloat16))
     flag = torch.tensor([1 if ok else 0])
     dist.all_reduce(flag, op=dist.ReduceOp.MIN)
@@ -61,8 +75,7 @@ def test_plan_dispatch_groups_by_owner():
     import __graft_entry__ as entry
     entry.load_package()
     ep = importlib.import_module("dsv4_b200.runtime.expert_parallel")
-    ids = torch.tensor([[5, 0], [2, 7], [1, 6]], dtype=torch.int32)
-    order, counts, local = ep.plan_dispatch(ids, 4, 2)
-    assert counts.tolist() == [3, 3]
-    assert order.tolist() == [1, 2, 4, 0, 3, 5]                        # stable inside a destination
-    assert local.tolist() == [0, 2, 1, 1, 3, 2]
+    ids = torch.tensor([[5, 0], [2, 3], [1, 6], [7, 4]], dtype=torch.int32)
+    token_of, counts = ep.plan_dispatch(ids, 4, 2)
+    assert counts.tolist() == [3, 3]                                   # token 1 only to rank 0, token 3 only to rank 1
+    assert token_of.tolist() == [0, 1, 2, 0, 2, 3]                     # rank 0's rows, then rank 1's; tokens ascending

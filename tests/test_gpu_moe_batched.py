@@ -82,3 +82,28 @@ def test_moe_forward_scale_invariance(rt, qz, path):
         got = out.float().cpu().numpy()
         assert np.isfinite(got).all()
         assert oracle.max_abs_rel(got, ref) <= 1e-2 and oracle.cosine(got, ref) >= 0.9999
+
+
+@pytest.mark.parametrize("path", ["mxf4", "fp16"])
+def test_moe_forward_skips_negative_ids(rt, qz, path):
+    """A negative id marks a pair to skip (how an expert-parallel rank masks the experts of other ranks): the result
+    is the layer without those pairs (oracle with their router weight set to zero); a token whose pairs are all
+    skipped gets zeros; the status word stays 0."""
+    dev = torch.device("cuda:0")
+    T, E, K, H, k = 40, 8, 256, 512, 4
+    bank = qz.make_expert_bank(E, K, H, "cpu", seed=21)
+    x = (torch.randn(T, K, generator=torch.Generator().manual_seed(3)) * 2.0).to(torch.bfloat16)
+    ids, w = routing(T, E, k, seed=6)
+    g = torch.Generator().manual_seed(7)
+    drop = torch.rand(T, k, generator=g) < 0.4
+    drop[5] = True                                                   # token 5: nothing local
+    masked = torch.where(drop, torch.full_like(ids, -1), ids)
+    out = rt.moe_forward({n: v.to(dev) for n, v in bank.items()}, x.to(dev), masked.to(dev), w.to(dev), path=path)
+    torch.cuda.synchronize()
+    assert rt.moe_device_status() == 0
+    w_kept = torch.where(drop, torch.zeros_like(w), w)
+    ref = oracle.moe_layer_ref(x, bank, ids.numpy(), w_kept.numpy())
+    got = out.float().cpu().numpy()
+    err, cos = oracle.max_abs_rel(got, ref), oracle.cosine(got, ref)
+    assert err <= 1e-2 and cos >= 0.9999, f"max-abs/inf {err:.3e} cosine {cos:.7f}"
+    assert not np.any(got[5])
