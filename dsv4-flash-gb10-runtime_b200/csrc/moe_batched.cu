@@ -126,8 +126,12 @@ static int moe_forward_impl(int path, const __nv_bfloat16* x, const uint8_t* ban
 
     int* status = nullptr;
     cudaGetSymbolAddress(reinterpret_cast<void**>(&status), g_device_status);
-    moe_group_kernel<<<1, 1024, 0, stream>>>(ids, P, n_experts, hidden, out_dim, path == 1 ? kQTokUp : kMoeTileTokens,
-                                             path == 1 ? kQTokDown : kMoeTileTokens, g, status);
+    if (path == 1)
+        moe_group_kernel<<<1, 1024, 0, stream>>>(ids, P, n_experts, hidden / kMoeTileRows,
+                                                 (out_dim + kQRowsDown - 1) / kQRowsDown, kQTokUp, kQTokDown, g, status);
+    else
+        moe_group_kernel<<<1, 1024, 0, stream>>>(ids, P, n_experts, hidden / kMoeTileRows, out_dim / kMoeTileRows,
+                                                 kMoeTileTokens, kMoeTileTokens, g, status);
     const int grid = sm_count();
 
     if (path == 1) {

@@ -12,8 +12,8 @@
 // accumulator, which the epilogue adds.  When 3n > 256 (the MMA's largest N) the third term moves to row 256 and
 // gets an MMA of its own.
 //
-// Tiles: 128 weight rows (M) of one matrix (down) or of W1 and W3 (gate/up, two accumulators) x up to kTok
-// tokens; a stage covers 256 K-elements (one 128-byte swizzled row per operand row = 4 MMAs of K = 64).  Per stage
+// Tiles: two blocks of 128 weight rows (two accumulators: rows m0.. of W1 and of W3 for gate/up, rows m0.. and
+// m0 + 128.. of W2 for down) x up to 64 tokens; a stage covers 256 K-elements (one 128-byte swizzled row per operand row = 4 MMAs of K = 64).  Per stage
 // the 16 producer warps copy with cp.async: the packed weight rows, the three packed activation terms of the
 // tile's tokens, and the scale bytes re-arranged into 512-byte scale atoms; one lane of the last warp copies the
 // atoms into tensor memory (tcgen05.cp) and issues the MMAs; tcgen05.commit releases the stage.  Persistent grid,
@@ -30,8 +30,9 @@ namespace dsv4 {
 constexpr int kQKBlock = 256;                        // K-elements per stage
 constexpr int kQTerms = 3;                           // activation terms
 constexpr uint32_t kQTile = 128 * 128;               // bytes of one packed weight tile (128 rows x 128 B)
-constexpr int kQTokUp = 64;                          // tokens per gate/up tile (3 x 64 = 192 accumulator columns x 2)
-constexpr int kQTokDown = 128;                       // tokens per down tile
+constexpr int kQTokUp = 64;                          // tokens per tile (3 x 64 = 192 accumulator columns x 2)
+constexpr int kQTokDown = 64;
+constexpr int kQRowsDown = 256;                      // W2 rows per down tile (two row blocks share the activation tile)
 
 struct MoeQGemmArgs {
     const uint8_t* wa_p; const uint8_t* wb_p;        // up: W1, W3 packed; down: W2
@@ -49,7 +50,7 @@ struct MoeQGemmArgs {
 
 template <int MODE>
 struct MoeQGemmLayout {
-    static constexpr int kMats = MODE == 0 ? 2 : 1;
+    static constexpr int kMats = 2;
     static constexpr int kTok = MODE == 0 ? kQTokUp : kQTokDown;
     static constexpr int kStages = 3;
     // rows of the stacked B operand: contiguous when the three terms fit one MMA, else term 3 at row 256
@@ -69,19 +70,19 @@ struct MoeQGemmLayout {
     static_assert(kAccCols + kStages * kSfColsPerStage <= 512, "tensor memory overflow");
     static_assert(kMats * 128 + kQTerms * kTok <= kGemmProducers, "one scale row per producer thread");
     static_assert(kBytes <= 227 * 1024, "shared memory overflow");
-    static_assert(kTok <= 128, "the drain handles at most two 16-token chunks per warp");
+    static_assert(kTok <= 64, "the drain handles one 16-token chunk per warp");
 };
 
 // What a tile is: expert, rows, tokens; identical in every thread of the CTA.
 struct MoeQTile {
-    int e, slot0, n_valid, n_mma, m0, term_row2;
+    int e, slot0, n_valid, n_mma, m0, term_row2, mats;
     bool split;
 };
 
 // tiles / offsets: the grouping kernel's prefix sums, staged in shared memory by the caller.
 template <int TOK>
 __device__ __forceinline__ MoeQTile moe_qtile_decode(const int* tiles, const int* offsets, int n_experts, int m_tiles,
-                                                     int tile) {
+                                                     int tile_rows, int rows, int tile) {
     int lo = 0, hi = n_experts;
     while (hi - lo > 1) {
         const int md = (lo + hi) >> 1;
@@ -94,7 +95,8 @@ __device__ __forceinline__ MoeQTile moe_qtile_decode(const int* tiles, const int
     t.slot0 = offsets[lo] + nt * TOK;
     t.n_valid = min(TOK, offsets[lo + 1] - t.slot0);
     t.n_mma = (t.n_valid + 15) & ~15;
-    t.m0 = mt * kMoeTileRows;
+    t.m0 = mt * tile_rows;
+    t.mats = (tile_rows == 2 * kMoeTileRows && t.m0 + kMoeTileRows >= rows) ? 1 : 2;   // a last, half down tile
     t.split = 3 * t.n_mma > 256;                       // B rows (= accumulator columns) of the three terms
     t.term_row2 = t.split ? 256 : 2 * t.n_mma;
     return t;
@@ -141,7 +143,9 @@ __global__ void __launch_bounds__(kGemmThreads, 1) moe_gemm_mxf4_kernel(const Mo
 
     const int* tiles = s_tiles;
     const int n_tiles = tiles[a.n_experts];
-    const int m_tiles = a.rows / kMoeTileRows;
+    // gate/up: 128 rows of W1 and the same 128 rows of W3; down: 256 rows of W2 (the last tile may hold 128)
+    const int tile_rows = MODE == 0 ? kMoeTileRows : kQRowsDown;
+    const int m_tiles = (a.rows + tile_rows - 1) / tile_rows;
     uint32_t it = 0, tile_count = 0;
     bool alive = true;
 
@@ -171,40 +175,36 @@ __global__ void __launch_bounds__(kGemmThreads, 1) moe_gemm_mxf4_kernel(const Mo
                 for (int i = 0; i < 16; ++i)
                     v[i] = (__uint_as_float(p0[i]) + __uint_as_float(p1[i])) + __uint_as_float(p2[i]);
             };
-            const int ca = (warp >> 2) * 16, cb = ca + 64;       // this warp's token chunks (TOK <= 128: at most two)
-            const bool has_a = ca < t.n_mma && alive, has_b = cb < t.n_mma && alive;
-            if (MODE == 0) {
+            const int ca = (warp >> 2) * 16;                      // this warp's 16 tokens (TOK <= 64: one chunk per warp)
+            const bool has_a = ca < t.n_mma && alive;
+            {
+                // both accumulators of this warp's 16 tokens: gate and up (SwiGLU), or two row blocks of W2
                 float g[16], u[16];
-                if (has_a) { load_sum(ca, g); load_sum(L::kAccStride + ca, u); }
-                hand_back();
                 if (has_a) {
+                    load_sum(ca, g);
+                    if (t.mats == 2) load_sum(L::kAccStride + ca, u);
+                    if (MODE == 1) {
 #pragma unroll
-                    for (int i = 0; i < 16; ++i)
-                        if (ca + i < t.n_valid)
-                            a.mid[(size_t)(t.slot0 + ca + i) * a.rows + t.m0 + r] = (g[i] / (1.0f + __expf(-g[i]))) * u[i];
-                }
-            } else {
-                float ga[16], gb[16];
-                if (has_a) {
-                    load_sum(ca, ga);
-#pragma unroll
-                    for (int i = 0; i < 16; ++i) ga[i] *= ca + i < t.n_valid ? w_of[ca + i] : 0.f;
-                }
-                if (has_b) {
-                    load_sum(cb, gb);
-#pragma unroll
-                    for (int i = 0; i < 16; ++i) gb[i] *= cb + i < t.n_valid ? w_of[cb + i] : 0.f;
+                        for (int i = 0; i < 16; ++i) {
+                            const float w = ca + i < t.n_valid ? w_of[ca + i] : 0.f;
+                            g[i] *= w;
+                            u[i] *= w;
+                        }
+                    }
                 }
                 hand_back();
                 if (has_a) {
 #pragma unroll
                     for (int i = 0; i < 16; ++i)
-                        if (ca + i < t.n_valid) a.y[(size_t)(t.slot0 + ca + i) * a.rows + t.m0 + r] = ga[i];
-                }
-                if (has_b) {
-#pragma unroll
-                    for (int i = 0; i < 16; ++i)
-                        if (cb + i < t.n_valid) a.y[(size_t)(t.slot0 + cb + i) * a.rows + t.m0 + r] = gb[i];
+                        if (ca + i < t.n_valid) {
+                            if (MODE == 0) {
+                                a.mid[(size_t)(t.slot0 + ca + i) * a.rows + t.m0 + r] = (g[i] / (1.0f + __expf(-g[i]))) * u[i];
+                            } else {
+                                float* yrow = a.y + (size_t)(t.slot0 + ca + i) * a.rows + t.m0 + r;
+                                yrow[0] = g[i];
+                                if (t.mats == 2) yrow[kMoeTileRows] = u[i];
+                            }
+                        }
                 }
             }
         };
@@ -213,7 +213,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) moe_gemm_mxf4_kernel(const Mo
         bool has_prev = false;
         const int drain_at = min(S, n_kb) - 1;        // the stage after whose issue the previous tile is drained
         for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x, ++tile_count) {
-            const MoeQTile t = moe_qtile_decode<TOK>(tiles, s_offsets, a.n_experts, m_tiles, tile);
+            const MoeQTile t = moe_qtile_decode<TOK>(tiles, s_offsets, a.n_experts, m_tiles, tile_rows, a.rows, tile);
             int* rows_of = tok_row[tile_count & 1];
             if (tid < t.n_valid) {
                 const int slot = t.slot0 + tid;
@@ -232,7 +232,9 @@ __global__ void __launch_bounds__(kGemmThreads, 1) moe_gemm_mxf4_kernel(const Mo
             for (int m = 0; m < MATS; ++m)
 #pragma unroll
                 for (int h = 0; h < 2; ++h)
-                    wsrc[m][h] = (m == 0 ? a.wa_p : a.wb_p) + t.e * a.stride_p + (long long)(t.m0 + wr[h]) * row_p + wc * 16;
+                    wsrc[m][h] = (MODE == 0 ? (m == 0 ? a.wa_p : a.wb_p) + t.e * a.stride_p + (long long)(t.m0 + wr[h]) * row_p
+                                            : a.wa_p + t.e * a.stride_p + (long long)(t.m0 + kMoeTileRows * m + wr[h]) * row_p) +
+                                 wc * 16;
             // activations: chunk (token, c) of each term
             const uint8_t* bsrc[kBChunks];
             bool bok[kBChunks], bwrite[kBChunks];
@@ -248,9 +250,11 @@ __global__ void __launch_bounds__(kGemmThreads, 1) moe_gemm_mxf4_kernel(const Mo
             bool sfok = false;
             if (tid < MATS * 128) {
                 const int m = tid >> 7, r = tid & 127;
-                sfsrc = (m == 0 ? a.wa_s : a.wb_s) + t.e * a.stride_s + (long long)(t.m0 + r) * row_s;
+                sfsrc = MODE == 0 ? (m == 0 ? a.wa_s : a.wb_s) + t.e * a.stride_s + (long long)(t.m0 + r) * row_s
+                                  : a.wa_s + t.e * a.stride_s + (long long)(t.m0 + kMoeTileRows * m + r) * row_s;
                 sfdst = L::kOffSfA + m * 1024 + tc05_scale_atom_offset(r, 0);
-                sfok = true;
+                sfok = m < t.mats;
+                if (!sfok) sfsrc = nullptr;
             } else if (tid < MATS * 128 + kQTerms * TOK) {
                 const int idx = tid - MATS * 128;
                 const int term = idx / TOK, n = idx - term * TOK;
@@ -277,10 +281,12 @@ __global__ void __launch_bounds__(kGemmThreads, 1) moe_gemm_mxf4_kernel(const Mo
                 const uint32_t stage = smem_u32(gemm_smem) + s * L::kStageBytes;
 #pragma unroll
                 for (int m = 0; m < MATS; ++m)
+                    if (m < t.mats) {
 #pragma unroll
-                    for (int h = 0; h < 2; ++h)
-                        asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(stage + m * kQTile + tc05_sw128_offset(wr[h], wc)),
-                                     "l"(wsrc[m][h] + (size_t)kb * 128) : "memory");
+                        for (int h = 0; h < 2; ++h)
+                            asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(stage + m * kQTile + tc05_sw128_offset(wr[h], wc)),
+                                         "l"(wsrc[m][h] + (size_t)kb * 128) : "memory");
+                    }
 #pragma unroll
                 for (int term = 0; term < kQTerms; ++term) {
                     const int base_row = term == 2 ? t.term_row2 : term * t.n_mma;
@@ -307,7 +313,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) moe_gemm_mxf4_kernel(const Mo
     } else {
         // ---- last warp: scale atoms into tensor memory, then the MMAs of the stage
         for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x, ++tile_count) {
-            const MoeQTile t = moe_qtile_decode<TOK>(tiles, s_offsets, a.n_experts, m_tiles, tile);
+            const MoeQTile t = moe_qtile_decode<TOK>(tiles, s_offsets, a.n_experts, m_tiles, tile_rows, a.rows, tile);
             const int n_first = t.split ? 2 * t.n_mma : 3 * t.n_mma;     // N of the first MMA
             const int groups = (t.term_row2 + t.n_mma + 127) >> 7;       // row groups of B scales in use
             if (tile_count > 0 && alive)                                 // previous accumulator drained?
@@ -325,7 +331,8 @@ __global__ void __launch_bounds__(kGemmThreads, 1) moe_gemm_mxf4_kernel(const Mo
                     for (int at = 0; at < 2; ++at) {
 #pragma unroll
                         for (int m = 0; m < MATS; ++m)
-                            tc05_copy_scale_atom(sfa_cols + m * 8 + at * 4, stage + L::kOffSfA + m * 1024 + at * 512);
+                            if (m < t.mats)
+                                tc05_copy_scale_atom(sfa_cols + m * 8 + at * 4, stage + L::kOffSfA + m * 1024 + at * 512);
 #pragma unroll
                         for (int g = 0; g < RG; ++g)
                             if (g < groups)
@@ -339,14 +346,15 @@ __global__ void __launch_bounds__(kGemmThreads, 1) moe_gemm_mxf4_kernel(const Mo
                         const uint64_t db = tc05_desc_k_sw128(stage + L::kOffB + 32 * j);
 #pragma unroll
                         for (int m = 0; m < MATS; ++m)
-                            tc05_mma_mxf4(tmem + m * L::kAccStride, tc05_desc_k_sw128(stage + m * kQTile + 32 * j), db,
-                                          idesc, sfa_cols + m * 8 + (j >> 1) * 4, sfb, acc);
+                            if (m < t.mats)
+                                tc05_mma_mxf4(tmem + m * L::kAccStride, tc05_desc_k_sw128(stage + m * kQTile + 32 * j), db,
+                                              idesc, sfa_cols + m * 8 + (j >> 1) * 4, sfb, acc);
                         if (t.split) {
                             const uint32_t idesc3 = tc05_idesc_mxf4(128, t.n_mma, (j & 1) * 2, (j & 1) * 2);
                             const uint64_t db3 = tc05_desc_k_sw128(stage + L::kOffB + 256 * 128 + 32 * j);
 #pragma unroll
                             for (int m = 0; m < MATS; ++m)
-                                tc05_mma_mxf4(tmem + m * L::kAccStride + 256,
+                                if (m < t.mats) tc05_mma_mxf4(tmem + m * L::kAccStride + 256,
                                               tc05_desc_k_sw128(stage + m * kQTile + 32 * j), db3, idesc3,
                                               sfa_cols + m * 8 + (j >> 1) * 4, sfb + 8, acc);
                         }

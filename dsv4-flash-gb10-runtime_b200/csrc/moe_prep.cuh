@@ -54,10 +54,10 @@ __global__ void moe_token_fp16_kernel(const __nv_bfloat16* __restrict__ x, int n
 }
 
 // Single CTA: counting sort of the P = n_tokens * k pairs by expert id.  The order of pairs inside an expert is
-// arbitrary (it only decides which accumulator column a token uses, not any arithmetic).  tok_up / tok_down:
-// tokens per gate/up and per down tile of the GEMM kernels that will read the tables.
+// arbitrary (it only decides which accumulator column a token uses, not any arithmetic).  tok_up / tok_down and
+// m_tiles_up / m_tiles_down: tokens per tile and row tiles per expert of the GEMM kernels that will read the tables.
 __global__ void __launch_bounds__(1024) moe_group_kernel(const int* __restrict__ ids, int n_pairs, int n_experts,
-                                                         int rows_up, int rows_down, int tok_up, int tok_down,
+                                                         int m_tiles_up, int m_tiles_down, int tok_up, int tok_down,
                                                          MoeGroups g, int* __restrict__ status) {
     __shared__ int count[kMoeMaxExperts];
     __shared__ int cursor[kMoeMaxExperts];
@@ -88,8 +88,7 @@ __global__ void __launch_bounds__(1024) moe_group_kernel(const int* __restrict__
         __shared__ int warp_sums[3][32];
         const int e = threadIdx.x, lane = e & 31, wid = e >> 5;
         const int c = e < n_experts ? count[e] : 0;
-        int v[3] = {c, ((c + tok_up - 1) / tok_up) * (rows_up / kMoeTileRows),
-                    ((c + tok_down - 1) / tok_down) * (rows_down / kMoeTileRows)};
+        int v[3] = {c, ((c + tok_up - 1) / tok_up) * m_tiles_up, ((c + tok_down - 1) / tok_down) * m_tiles_down};
         int inc[3];
 #pragma unroll
         for (int q = 0; q < 3; ++q) {
