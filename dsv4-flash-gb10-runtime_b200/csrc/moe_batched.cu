@@ -73,6 +73,36 @@ cudaError_t allow_smem(Kernel kernel, size_t bytes, int (&done)[64]) {
 
 bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
+// DSV4_B200_PDL=0 switches programmatic dependent launch off (debugging).
+bool pdl_enabled() {
+    static int v = -1;
+    if (v < 0) {
+        const char* e = std::getenv("DSV4_B200_PDL");
+        v = (e && e[0] == '0') ? 0 : 1;
+    }
+    return v == 1;
+}
+
+// Every kernel of this library starts with griddepcontrol.launch_dependents and reads or writes global memory only
+// after griddepcontrol.wait, so consecutive kernels are launched with programmatic stream serialisation: the
+// next kernel's CTAs are scheduled while the previous kernel drains, and its prologue (barrier set-up, tensor
+// memory allocation) overlaps the tail.
+template <class... Params, class... Args>
+cudaError_t launch_k(void (*kernel)(Params...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                     Args&&... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = pdl_enabled() ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kernel, std::forward<Args>(args)...);
+}
+
 }  // namespace
 
 // Bytes of workspace mxfp4_moe_forward needs (normalised activations, grouping tables, the fp16 intermediate
@@ -127,11 +157,11 @@ static int moe_forward_impl(int path, const __nv_bfloat16* x, const uint8_t* ban
     int* status = nullptr;
     cudaGetSymbolAddress(reinterpret_cast<void**>(&status), g_device_status);
     if (path == 1)
-        moe_group_kernel<<<1, 1024, 0, stream>>>(ids, P, n_experts, hidden / kMoeTileRows,
-                                                 (out_dim + kQRowsDown - 1) / kQRowsDown, kQTokUp, kQTokDown, g, status);
+        launch_k(moe_group_kernel, dim3(1), dim3(1024), 0, stream, ids, P, n_experts, hidden / kMoeTileRows,
+                 (out_dim + kQRowsDown - 1) / kQRowsDown, kQTokUp, kQTokDown, g, status);
     else
-        moe_group_kernel<<<1, 1024, 0, stream>>>(ids, P, n_experts, hidden / kMoeTileRows, out_dim / kMoeTileRows,
-                                                 kMoeTileTokens, kMoeTileTokens, g, status);
+        launch_k(moe_group_kernel, dim3(1), dim3(1024), 0, stream, ids, P, n_experts, hidden / kMoeTileRows,
+                 out_dim / kMoeTileRows, kMoeTileTokens, kMoeTileTokens, g, status);
     const int grid = sm_count();
 
     if (path == 1) {
@@ -141,7 +171,7 @@ static int moe_forward_impl(int path, const __nv_bfloat16* x, const uint8_t* ban
         uint8_t* mq = ws + m.mq; uint8_t* ms = ws + m.ms;
         float* midf = reinterpret_cast<float*>(ws + m.midf);
         const int qgrid = 4 * grid;
-        moe_quantize_mxfp4x3_kernel<__nv_bfloat16><<<qgrid, 256, 0, stream>>>(x, n_tokens, K_in, xq, xs);
+        launch_k(moe_quantize_mxfp4x3_kernel<__nv_bfloat16>, dim3(qgrid), dim3(256), 0, stream, x, n_tokens, K_in, xq, xs);
         MoeQGemmArgs qu;
         qu.wa_p = bank_W1_packed; qu.wb_p = bank_W3_packed; qu.wa_s = bank_W1_scale; qu.wb_s = bank_W3_scale;
         qu.stride_p = (long long)hidden * (K_in / 2); qu.stride_s = (long long)hidden * (K_in / 32);
@@ -149,8 +179,8 @@ static int moe_forward_impl(int path, const __nv_bfloat16* x, const uint8_t* ban
         qu.act_q = xq; qu.act_s = xs; qu.act_rows = n_tokens; qu.pair_w = weights; qu.g = g; qu.mid = midf; qu.y = nullptr;
         cudaError_t qerr = allow_smem(moe_gemm_mxf4_kernel<0>, MoeQGemmLayout<0>::kBytes, qup_done);
         if (qerr == cudaSuccess) {
-            moe_gemm_mxf4_kernel<0><<<grid, kGemmThreads, MoeQGemmLayout<0>::kBytes, stream>>>(qu);
-            moe_quantize_mxfp4x3_kernel<float><<<qgrid, 256, 0, stream>>>(midf, (long long)P, hidden, mq, ms);
+            launch_k(moe_gemm_mxf4_kernel<0>, dim3(grid), dim3(kGemmThreads), MoeQGemmLayout<0>::kBytes, stream, qu);
+            launch_k(moe_quantize_mxfp4x3_kernel<float>, dim3(qgrid), dim3(256), 0, stream, midf, (long long)P, hidden, mq, ms);
             qerr = cudaGetLastError();
         }
         MoeQGemmArgs qd = qu;
@@ -159,9 +189,9 @@ static int moe_forward_impl(int path, const __nv_bfloat16* x, const uint8_t* ban
         qd.rows = out_dim; qd.K = hidden; qd.act_q = mq; qd.act_s = ms; qd.act_rows = P; qd.mid = nullptr; qd.y = y;
         if (qerr == cudaSuccess) qerr = allow_smem(moe_gemm_mxf4_kernel<1>, MoeQGemmLayout<1>::kBytes, qdown_done);
         if (qerr == cudaSuccess) {
-            moe_gemm_mxf4_kernel<1><<<grid, kGemmThreads, MoeQGemmLayout<1>::kBytes, stream>>>(qd);
+            launch_k(moe_gemm_mxf4_kernel<1>, dim3(grid), dim3(kGemmThreads), MoeQGemmLayout<1>::kBytes, stream, qd);
             dim3 cgrid((out_dim / 4 + 127) / 128, n_tokens);
-            moe_combine_kernel<<<cgrid, 128, 0, stream>>>(y, g.pair_slot, n_tokens, k, out_dim, out);
+            launch_k(moe_combine_kernel, dim3(cgrid), dim3(128), 0, stream, y, g.pair_slot, n_tokens, k, out_dim, out);
             qerr = cudaGetLastError();
         }
         if (qerr != cudaSuccess) {
@@ -172,7 +202,7 @@ static int moe_forward_impl(int path, const __nv_bfloat16* x, const uint8_t* ban
     }
 
     // ---- fp16 tensor-core path with in-kernel dequantisation
-    moe_token_fp16_kernel<<<(n_tokens + 7) / 8, 256, 0, stream>>>(x, n_tokens, K_in, xh, xexp);
+    launch_k(moe_token_fp16_kernel, dim3((n_tokens + 7) / 8), dim3(256), 0, stream, x, n_tokens, K_in, xh, xexp);
     MoeGemmArgs up;
     up.wa_p = bank_W1_packed; up.wb_p = bank_W3_packed; up.wa_s = bank_W1_scale; up.wb_s = bank_W3_scale;
     up.stride_p = (long long)hidden * (K_in / 2); up.stride_s = (long long)hidden * (K_in / 32);
@@ -181,7 +211,7 @@ static int moe_forward_impl(int path, const __nv_bfloat16* x, const uint8_t* ban
     const size_t smem_up = MoeGemmLayout<0>::bytes(K_in);
     cudaError_t err = allow_smem(moe_gemm_kernel<0>, smem_up, up_done);
     if (err == cudaSuccess) {
-        moe_gemm_kernel<0><<<grid, kGemmThreads, smem_up, stream>>>(up);
+        launch_k(moe_gemm_kernel<0>, dim3(grid), dim3(kGemmThreads), smem_up, stream, up);
         err = cudaGetLastError();
     }
     MoeGemmArgs down = up;
@@ -191,12 +221,12 @@ static int moe_forward_impl(int path, const __nv_bfloat16* x, const uint8_t* ban
     const size_t smem_down = MoeGemmLayout<1>::bytes(hidden);
     if (err == cudaSuccess) err = allow_smem(moe_gemm_kernel<1>, smem_down, down_done);
     if (err == cudaSuccess) {
-        moe_gemm_kernel<1><<<grid, kGemmThreads, smem_down, stream>>>(down);
+        launch_k(moe_gemm_kernel<1>, dim3(grid), dim3(kGemmThreads), smem_down, stream, down);
         err = cudaGetLastError();
     }
     if (err == cudaSuccess) {
         dim3 cgrid((out_dim / 4 + 127) / 128, n_tokens);
-        moe_combine_kernel<<<cgrid, 128, 0, stream>>>(y, g.pair_slot, n_tokens, k, out_dim, out);
+        launch_k(moe_combine_kernel, dim3(cgrid), dim3(128), 0, stream, y, g.pair_slot, n_tokens, k, out_dim, out);
         err = cudaGetLastError();
     }
     if (err != cudaSuccess) {
