@@ -11,9 +11,10 @@
 //
 // 16 warps per CTA.  Each warp owns a private 8.5 KB ring: two slots of one (W1 row, W3 row, 2 scale rows) pair in
 // the first phase, two slots of four (W2 row, scale row) in the second (4 352 bytes per slot in both: the fixed
-// cost of a task - wait, butterfly reduction, claim, refill - is paid once per 4 KB of weights).  Second-phase work
-// is cut into (expert, 4-row chunk) tasks numbered expert-major and claimed from a shared counter; a warp reloads
-// its blocks of the expert's fp16 intermediate from shared memory only when it crosses into another expert.
+// cost of a task - wait, butterfly reduction, refill - is paid once per 4 KB of weights).  The second phase splits
+// the CTA's (expert, output row) units evenly over the warps; a warp walks its range in tasks of up to four rows of
+// one expert and reloads its blocks of the expert's fp16 intermediate from shared memory only when it crosses into
+// another expert.
 #pragma once
 
 #include "grouped_ring.cuh"
@@ -93,7 +94,7 @@ __global__ void __launch_bounds__(kFusedWarps * 32, 1) moe_decode_fused_kernel(c
     __shared__ int expert_of_slot[8];
     __shared__ float weight_of_slot[8];
     __shared__ float mid_scale[8];
-    __shared__ int next_pair, next_task;          // work queues of the two phases
+    __shared__ int next_pair;                     // work queue of the first phase
     pdl_launch_dependents();
 
     const int lane = threadIdx.x & 31;
@@ -119,7 +120,7 @@ __global__ void __launch_bounds__(kFusedWarps * 32, 1) moe_decode_fused_kernel(c
     const long long total = (long long)a.E << h_shift;
     const int q_begin = (int)(total * blockIdx.x / gridDim.x);
     const int q_end = (int)(total * (blockIdx.x + 1) / gridDim.x);
-    if (threadIdx.x == 0) { next_pair = q_begin; next_task = 0; }
+    if (threadIdx.x == 0) next_pair = q_begin;
     // work is handed out from a shared counter at the moment a ring slot is (re)filled, so that the warps of a
     // CTA finish together
     auto claim = [&](int* counter) -> int {
@@ -242,17 +243,28 @@ __global__ void __launch_bounds__(kFusedWarps * 32, 1) moe_decode_fused_kernel(c
     const int o_begin = (int)((long long)a.O * blockIdx.x / gridDim.x);
     const int o_end = (int)((long long)a.O * (blockIdx.x + 1) / gridDim.x);
     const int n_local = o_end - o_begin;
-    const int n_chunks = (n_local + R - 1) / R;
-    const int n_tasks = a.E * n_chunks;                              // task t: expert t / n_chunks, chunk t % n_chunks
-    // t / n_chunks == (t * inv_c) >> 16: exact for t < 256 and n_chunks <= 32 (E <= 8, at most 64 rows per CTA)
-    const uint32_t inv_c = (65536u + n_chunks - 1) / n_chunks;
+    // The CTA's (expert, output row) units, expert-major, are split evenly over the warps (10.5 each at the DSv4
+    // shape: every warp finishes at the same time); a warp walks its range in tasks of up to R rows of one expert.
+    // A task is packed as expert << 16 | first row << 8 | rows; 0 = none.
+    const int n_units = a.E * n_local;
+    int u_next = (int)((long long)n_units * warp / NW);
+    const int u_end = (int)((long long)n_units * (warp + 1) / NW);
+    // u / n_local == (u * inv_n) >> 16: exact for u < 512 and n_local <= 64 (E <= 8, at most 64 rows per CTA)
+    const uint32_t inv_n = (65536u + n_local - 1) / n_local;
+    auto next_task = [&]() -> int {
+        if (u_next >= u_end) return 0;
+        const int e = (int)(((uint32_t)u_next * inv_n) >> 16);
+        const int l0 = u_next - e * n_local;
+        const int rows = min(min(R, n_local - l0), u_end - u_next);
+        u_next += rows;
+        return (e << 16) | (l0 << 8) | rows;
+    };
 
     auto issue_b = [&](int t, int s) {
         if (lane < 2) {
-            const int e = (int)(((uint32_t)t * inv_c) >> 16);
-            const int l0 = (t - e * n_chunks) * R;
+            const int e = t >> 16, l0 = (t >> 8) & 255;
+            const uint32_t rows = (uint32_t)(t & 255);
             const long long eid = (long long)expert_of_slot[e];
-            const uint32_t rows = (uint32_t)min(R, n_local - l0);
             const bool scale = lane == 1;
             const uint32_t rb = scale ? L::kRowSB : L::kRowPB;
             const uint8_t* src = (scale ? a.w2s + eid * a.strideBs : a.w2p + eid * a.strideBp) +
@@ -268,8 +280,8 @@ __global__ void __launch_bounds__(kFusedWarps * 32, 1) moe_decode_fused_kernel(c
     // could not start before the whole ring had arrived.  The other slots follow once the loads of the
     // intermediate are in flight.
     int tb[SB];
-    tb[0] = claim(&next_task);
-    if (tb[0] < n_tasks && alive) issue_b(tb[0], 0);
+    tb[0] = next_task();
+    if (tb[0] != 0 && alive) issue_b(tb[0], 0);
 
     // grid barrier, second half: every SwiGLU row of every expert is written
     if (arbiter) barrier_ok = fused_barrier_wait(barrier_base, gridDim.x * NW) ? 1 : 0;
@@ -292,8 +304,8 @@ __global__ void __launch_bounds__(kFusedWarps * 32, 1) moe_decode_fused_kernel(c
         }
 #pragma unroll
         for (int s = 1; s < SB; ++s) {                               // the rest of the ring
-            tb[s] = claim(&next_task);
-            if (tb[s] < n_tasks && alive) issue_b(tb[s], s);
+            tb[s] = next_task();
+            if (tb[s] != 0 && alive) issue_b(tb[s], s);
         }
 #pragma unroll
         for (int p = 0; p < kPieces; ++p) {
@@ -333,10 +345,9 @@ __global__ void __launch_bounds__(kFusedWarps * 32, 1) moe_decode_fused_kernel(c
 #pragma unroll
             for (int s = 0; s < SB; ++s) {
                 const int t = tb[s];
-                if (t < n_tasks && alive) {
+                if (t != 0 && alive) {
                     any = true;
-                    const int e = (int)(((uint32_t)t * inv_c) >> 16);
-                    const int l0 = (t - e * n_chunks) * R;
+                    const int e = t >> 16, l0 = (t >> 8) & 255, rows = t & 255;
                     if (e != cur_e) { lane_blocks_from_smem<L::kBplB>(vec + (size_t)e * HT, lane, m2); cur_e = e; }
                     alive = mbar_wait_bounded(bars_b + 8 * s, parity, 2);
                     float v[R];
@@ -352,12 +363,12 @@ __global__ void __launch_bounds__(kFusedWarps * 32, 1) moe_decode_fused_kernel(c
                     }
                     multi_reduce<R>(v, lane);
                     if (multi_reduce_owner<R>(lane) && alive) {
-                        const int l = l0 + multi_reduce_index<R>(lane);
-                        if (l < n_local) part[l][e] = v[0] * mid_scale[e];   // rows past the chunk hold stale bytes
+                        const int idx = multi_reduce_index<R>(lane);
+                        if (idx < rows) part[l0 + idx][e] = v[0] * mid_scale[e];   // rows past the task hold stale bytes
                     }
                     __syncwarp();                                    // every lane has read the slot
-                    tb[s] = claim(&next_task);
-                    if (tb[s] < n_tasks && alive) issue_b(tb[s], s);
+                    tb[s] = next_task();
+                    if (tb[s] != 0 && alive) issue_b(tb[s], s);
                 }
             }
         }
