@@ -16,6 +16,9 @@
 // one expert and reloads its blocks of the expert's fp16 intermediate from shared memory only when it crosses into
 // another expert.
 #pragma once
+#ifndef DSV4_EXP_PREFETCH_BEFORE
+#define DSV4_EXP_PREFETCH_BEFORE 1
+#endif
 
 #include "grouped_ring.cuh"
 
@@ -280,8 +283,10 @@ __global__ void __launch_bounds__(kFusedWarps * 32, 1) moe_decode_fused_kernel(c
     // could not start before the whole ring had arrived.  The other slots follow once the loads of the
     // intermediate are in flight.
     int tb[SB];
+#if DSV4_EXP_PREFETCH_BEFORE
     tb[0] = next_task();
     if (tb[0] != 0 && alive) issue_b(tb[0], 0);
+#endif
 
     // grid barrier, second half: every SwiGLU row of every expert is written
     if (arbiter) barrier_ok = fused_barrier_wait(barrier_base, gridDim.x * NW) ? 1 : 0;
@@ -303,7 +308,7 @@ __global__ void __launch_bounds__(kFusedWarps * 32, 1) moe_decode_fused_kernel(c
             if (idx8 < n8) load8_as_float(a.mid + (size_t)idx8 * 8, v[p]);
         }
 #pragma unroll
-        for (int s = 1; s < SB; ++s) {                               // the rest of the ring
+        for (int s = DSV4_EXP_PREFETCH_BEFORE ? 1 : 0; s < SB; ++s) {                               // the rest of the ring
             tb[s] = next_task();
             if (tb[s] != 0 && alive) issue_b(tb[s], s);
         }
