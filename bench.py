@@ -303,6 +303,66 @@ def batched_small(rt, torch, bank, dev, T, steps, warmup):
                       "tflops": T * TOP_K * 2 * 3 * HIDDEN * EXPERT_FF / ms / 1e9}), flush=True)
 
 
+def dense_configs(rt, qz, torch, dev):
+    """Configurations 0 and 1 (MXFP4 dense GEMV [2048 x 4096]; FP8-E4M3 dense GEMV [8192 x 4096], E8M0 and FP32
+    block scales) as side measurements: every call of a replayed CUDA graph reads another copy of the weights, and
+    the copies together are larger than twice the L2."""
+    peak = measured_hbm_peak()[0]
+    out = {}
+    g = torch.Generator(device=dev).manual_seed(1234)
+    x = torch.randn(HIDDEN, generator=g, device=dev).to(torch.bfloat16)
+
+    def timed(calls, bytes_per_call):
+        stream = torch.cuda.Stream(device=dev)
+        with torch.cuda.stream(stream):
+            for c in calls[:3]:
+                c()
+            stream.synchronize()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, stream=stream):
+                for c in calls:
+                    c()
+            for _ in range(5):
+                graph.replay()
+            stream.synchronize()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            reps = 20
+            a.record(stream)
+            for _ in range(reps):
+                graph.replay()
+            b.record(stream)
+            stream.synchronize()
+        us = a.elapsed_time(b) * 1e3 / (reps * len(calls))
+        gbs = bytes_per_call / us / 1e3
+        return {"us_per_call": us, "gbs": gbs, "frac_of_measured_hbm_peak": gbs / peak, "weight_copies": len(calls),
+                "bytes_per_call": bytes_per_call}
+
+    # config 0
+    n0, copies0 = 2048, 64
+    w = (torch.randn(copies0 * n0, HIDDEN, generator=g, device=dev) * 0.02)
+    wp, ws = qz.quantize_mxfp4(w)
+    del w
+    wp, ws = wp.view(copies0, n0, HIDDEN // 2), ws.view(copies0, n0, HIDDEN // 32)
+    y0 = torch.empty(n0, dtype=torch.bfloat16, device=dev)
+    stream_calls = [(lambda i=i: rt.mxfp4_gemv(wp[i], ws[i], x, out=y0)) for i in range(copies0)]
+    out["config0_mxfp4_dense_gemv_2048x4096"] = timed(stream_calls, n0 * HIDDEN // 2 + n0 * HIDDEN // 32 + HIDDEN * 2 + n0 * 2)
+    del wp, ws
+    # config 1
+    n1, copies1 = 8192, 10
+    y1 = torch.empty(n1, dtype=torch.bfloat16, device=dev)
+    for kind, fn, scale_bytes in (("e8m0", rt.fp8_e4m3_gemv, 1), ("f32", rt.fp8_e4m3_gemv_f32scale, 4)):
+        mats = []
+        for i in range(copies1):
+            wq, sq = qz.quantize_fp8_block128(torch.randn(n1, HIDDEN, generator=g, device=dev) * 0.02, kind)
+            mats.append((wq, sq))
+        calls = [(lambda m=m: fn(m[0], m[1], x, out=y1)) for m in mats]
+        nbytes = n1 * HIDDEN + (n1 // 128) * (HIDDEN // 128) * scale_bytes + HIDDEN * 2 + n1 * 2
+        out[f"config1_fp8_dense_gemv_8192x4096_{kind}_scales"] = timed(calls, nbytes)
+        del mats, calls
+    torch.cuda.empty_cache()
+    return out
+
+
 def run_gpu(args, rank: int, world: int, local_rank: int):
     import torch
     import torch.distributed as dist
@@ -435,6 +495,9 @@ def run_gpu(args, rank: int, world: int, local_rank: int):
 
     if gb.device_status() != 0:
         raise RuntimeError("a kernel gave up on a bounded wait during the benchmark")
+    dense = None
+    if n_experts == N_EXPERTS and not args.no_batched and rank == 0:
+        dense = dense_configs(rt, qz, torch, dev)
     batched = None
     if n_experts == N_EXPERTS and not args.no_batched:
         if world > 1:      # the expert-parallel runs need the same bank on every rank before it is sharded
@@ -479,6 +542,8 @@ def run_gpu(args, rank: int, world: int, local_rank: int):
     }
     if batched is not None:
         line["batched"] = batched
+    if dense is not None:
+        line["dense"] = dense
     if world == 1:
         line["cpu_baseline"] = cpu_baseline(qz)
     print(json.dumps(line), flush=True)

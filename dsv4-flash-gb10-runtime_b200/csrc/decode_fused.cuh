@@ -16,6 +16,9 @@
 // one expert and reloads its blocks of the expert's fp16 intermediate from shared memory only when it crosses into
 // another expert.
 #pragma once
+#ifndef DSV4_EXP_POLL_PER_WARP
+#define DSV4_EXP_POLL_PER_WARP 0
+#endif
 #ifndef DSV4_EXP_PREFETCH_BEFORE
 #define DSV4_EXP_PREFETCH_BEFORE 1
 #endif
@@ -289,9 +292,20 @@ __global__ void __launch_bounds__(kFusedWarps * 32, 1) moe_decode_fused_kernel(c
 #endif
 
     // grid barrier, second half: every SwiGLU row of every expert is written
+#if DSV4_EXP_POLL_PER_WARP
+    {
+        // every warp polls for itself (16 staggered pollers per CTA see the last arrival sooner than one) and goes
+        // on to load the intermediate without a CTA-wide barrier; the staging below synchronises the CTA anyway
+        int ok = 1;
+        if (lane == 0) ok = fused_barrier_wait(barrier_base, gridDim.x * NW) ? 1 : 0;
+        ok = __shfl_sync(kFullMask, ok, 0);
+        if (!ok) alive = false;
+    }
+#else
     if (arbiter) barrier_ok = fused_barrier_wait(barrier_base, gridDim.x * NW) ? 1 : 0;
     __syncthreads();
     if (!barrier_ok) alive = false;
+#endif
 
     // intermediates -> fp16, one scale per expert, once per CTA
     {
