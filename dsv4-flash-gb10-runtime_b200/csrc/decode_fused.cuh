@@ -16,12 +16,6 @@
 // one expert and reloads its blocks of the expert's fp16 intermediate from shared memory only when it crosses into
 // another expert.
 #pragma once
-#ifndef DSV4_EXP_POLL_PER_WARP
-#define DSV4_EXP_POLL_PER_WARP 0
-#endif
-#ifndef DSV4_EXP_PREFETCH_BEFORE
-#define DSV4_EXP_PREFETCH_BEFORE 1
-#endif
 
 #include "grouped_ring.cuh"
 
@@ -32,8 +26,7 @@ constexpr int kFusedStagesA = 2;
 constexpr int kFusedRowsB = 4;
 constexpr int kFusedCap = 64;          // output rows per CTA
 
-// Grid barrier of the fused kernel, split into ARRIVE and WAIT so that a CTA can queue its next weight copies in
-// between.  Every warp arrives on its own with a fire-and-forget release increment of a counter that only grows;
+// Grid barrier of the fused kernel.  Every warp arrives on its own with a fire-and-forget release increment of a counter that only grows;
 // one lane per CTA waits until the counter has moved `arrivals` past the base it had when the grid started.  The
 // base is kept in device memory and advanced by the last CTA to leave the kernel, off the critical path (the next
 // grid reads it only after this one has completed).  Critical chain: the last warp's release increment, then one
@@ -281,31 +274,16 @@ __global__ void __launch_bounds__(kFusedWarps * 32, 1) moe_decode_fused_kernel(c
             bulk_copy_g2s(dst, src, rows * rb, bar);
         }
     };
-    // Only the first slot of every warp is requested before the barrier: loads issued behind a full ring of queued
-    // copies (the barrier's polls, the intermediate) would wait for all of them, and the arithmetic of this phase
-    // could not start before the whole ring had arrived.  The other slots follow once the loads of the
-    // intermediate are in flight.
+    // No W2 row is requested before the barrier: loads issued behind queued copies (the barrier's polls, the
+    // intermediate) wait for all of them.  The ring is filled once the loads of the intermediate are in flight;
+    // its first rows land while the intermediate is being converted.
     int tb[SB];
-#if DSV4_EXP_PREFETCH_BEFORE
-    tb[0] = next_task();
-    if (tb[0] != 0 && alive) issue_b(tb[0], 0);
-#endif
 
     // grid barrier, second half: every SwiGLU row of every expert is written
-#if DSV4_EXP_POLL_PER_WARP
-    {
-        // every warp polls for itself (16 staggered pollers per CTA see the last arrival sooner than one) and goes
-        // on to load the intermediate without a CTA-wide barrier; the staging below synchronises the CTA anyway
-        int ok = 1;
-        if (lane == 0) ok = fused_barrier_wait(barrier_base, gridDim.x * NW) ? 1 : 0;
-        ok = __shfl_sync(kFullMask, ok, 0);
-        if (!ok) alive = false;
-    }
-#else
+    // (one poller per CTA: with one per warp the polls slow the arrivals down - 29 us per layer instead of 23)
     if (arbiter) barrier_ok = fused_barrier_wait(barrier_base, gridDim.x * NW) ? 1 : 0;
     __syncthreads();
     if (!barrier_ok) alive = false;
-#endif
 
     // intermediates -> fp16, one scale per expert, once per CTA
     {
@@ -322,7 +300,7 @@ __global__ void __launch_bounds__(kFusedWarps * 32, 1) moe_decode_fused_kernel(c
             if (idx8 < n8) load8_as_float(a.mid + (size_t)idx8 * 8, v[p]);
         }
 #pragma unroll
-        for (int s = DSV4_EXP_PREFETCH_BEFORE ? 1 : 0; s < SB; ++s) {                               // the rest of the ring
+        for (int s = 0; s < SB; ++s) {                               // the W2 ring
             tb[s] = next_task();
             if (tb[s] != 0 && alive) issue_b(tb[s], s);
         }
