@@ -5,3 +5,4 @@ from .mxfp4_grouped_gemv_binding import (                                    # n
     mxfp4_grouped_gemv, mxfp4_grouped_gemv_static, mxfp4_grouped_gemv_ids, mxfp4_dequant_bf16, moe_route_topk, device_status,
     moe_decode_layer, decode_workspace_bytes, decode_picks)
 from .moe_batched import moe_forward, forward_workspace_bytes, moe_device_status   # noqa: F401
+from .bank_loader import load_expert_bank, load_shared_expert_fp8, SnapshotReader   # noqa: F401
