@@ -359,6 +359,32 @@ def dense_configs(rt, qz, torch, dev):
         nbytes = n1 * HIDDEN + (n1 // 128) * (HIDDEN // 128) * scale_bytes + HIDDEN * 2 + n1 * 2
         out[f"config1_fp8_dense_gemv_8192x4096_{kind}_scales"] = timed(calls, nbytes)
         del mats, calls
+    # the shared expert's gated FFN, all FP8 (W1, W3 [2048 x 4096], W2 [4096 x 2048]): fused entry and the three
+    # GEMV calls + activation it replaces
+    copies2 = 12
+    banks = []
+    for i in range(copies2):
+        sh = {}
+        for name, rows, cols in (("w1", EXPERT_FF, HIDDEN), ("w3", EXPERT_FF, HIDDEN), ("w2", HIDDEN, EXPERT_FF)):
+            sh[name], sh[name + "s"] = qz.quantize_fp8_block128(torch.randn(rows, cols, generator=g, device=dev) * 0.02, "e8m0")
+        banks.append(sh)
+    y2 = torch.empty(HIDDEN, dtype=torch.bfloat16, device=dev)
+    ws2 = torch.empty(EXPERT_FF * 2, dtype=torch.uint8, device=dev)
+    gbuf = torch.empty(EXPERT_FF, dtype=torch.bfloat16, device=dev)
+    ubuf = torch.empty(EXPERT_FF, dtype=torch.bfloat16, device=dev)
+
+    def three_calls(sh):
+        rt.fp8_e4m3_gemv(sh["w1"], sh["w1s"], x, out=gbuf)
+        rt.fp8_e4m3_gemv(sh["w3"], sh["w3s"], x, out=ubuf)
+        gf = gbuf.float().clamp_(-10.0, 10.0)
+        act = (torch.nn.functional.silu(gf) * ubuf.float()).to(torch.bfloat16)
+        rt.fp8_e4m3_gemv(sh["w2"], sh["w2s"], act, out=y2)
+
+    shared_bytes = 3 * EXPERT_FF * HIDDEN + 3 * (EXPERT_FF // 128) * (HIDDEN // 128) + 2 * HIDDEN * 2
+    out["shared_expert_fp8_swiglu_fused"] = timed(
+        [(lambda sh=sh: rt.fp8_shared_swiglu(sh, x, out=y2, workspace=ws2)) for sh in banks], shared_bytes)
+    out["shared_expert_fp8_swiglu_three_gemv_calls"] = timed([(lambda sh=sh: three_calls(sh)) for sh in banks], shared_bytes)
+    del banks
     torch.cuda.empty_cache()
     return out
 

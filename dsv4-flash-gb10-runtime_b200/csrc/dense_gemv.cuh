@@ -133,6 +133,68 @@ __global__ void __launch_bounds__(kDenseThreads, 2) dense_gemv_kernel(const Dens
     }
 }
 
+// Gate / up pair of a gated FFN with one token: act[n] = bf16( silu(clamp(g[n])) * clamp(u[n]) ), g = Wg x, u = Wu x,
+// both rounded to bf16 first (as two separate GEMV calls would leave them).  Same streaming scheme as
+// dense_gemv_kernel; a CTA owns a range of n and walks it once per matrix, so g[n] and u[n] meet in its shared memory.
+// limit_g / limit_u <= 0 switch the clamp of that operand off.
+constexpr int kDualCap = kDenseCap / 2;      // n per CTA
+
+template <class Fmt, class Sc>
+__global__ void __launch_bounds__(kDenseThreads, 2) dense_dual_swiglu_kernel(const DenseArgs ag, const DenseArgs au,
+                                                                             float limit_g, float limit_u) {
+    __shared__ float part[kDenseCap][kDenseMaxSlices];      // rows [0, kDualCap): gate, [kDualCap, 2 kDualCap): up
+    pdl_launch_dependents();
+
+    const int lane = threadIdx.x & 31;
+    const int warp = threadIdx.x >> 5;
+    const int n_warps = blockDim.x >> 5;
+    const int n_blk = ag.K / Fmt::kElems;
+    const int n_slices = (n_blk + 31) >> 5;
+    const int n_groups = max(1, n_warps / n_slices);
+    const int n_tasks = n_slices * n_groups;
+
+    const int r_begin = (int)((long long)ag.N * blockIdx.x / gridDim.x);
+    const int r_end = (int)((long long)ag.N * (blockIdx.x + 1) / gridDim.x);
+    const int n_local = r_end - r_begin;
+    const int span = kDenseRows * n_groups;
+
+    bool waited = false;
+    for (int task = warp; task < n_tasks; task += n_warps) {
+        const int ks = task % n_slices;
+        const int rg = task / n_slices;
+        const int blk = ks * 32 + lane;
+        const bool lane_ok = blk < n_blk;
+        ActBlock<Fmt> xb;
+#pragma unroll
+        for (int m = 0; m < 2; ++m) {
+            const DenseArgs& a = m == 0 ? ag : au;
+            float (*pm)[kDenseMaxSlices] = part + m * kDualCap;
+            DenseBatch b0, b1;
+            dense_issue<Sc>(a, r_begin + rg, n_groups, r_end, blk, lane_ok, b0);
+            if (!waited) { pdl_wait(); waited = true; }
+            if (m == 0) act_block_load_bf16<Fmt>(a.x + (size_t)blk * Fmt::kElems, lane_ok, xb);
+            for (int local0 = rg; local0 < n_local; local0 += 2 * span) {
+                dense_issue<Sc>(a, r_begin + local0 + span, n_groups, r_end, blk, lane_ok, b1);
+                dense_consume<Fmt, Sc>(b0, xb, lane, local0, n_groups, n_local, ks, pm);
+                dense_issue<Sc>(a, r_begin + local0 + 2 * span, n_groups, r_end, blk, lane_ok, b0);
+                dense_consume<Fmt, Sc>(b1, xb, lane, local0 + span, n_groups, n_local, ks, pm);
+            }
+        }
+    }
+    if (!waited) pdl_wait();
+    __syncthreads();
+
+    for (int t = threadIdx.x; t < n_local; t += blockDim.x) {
+        float g = 0.f, u = 0.f;
+        for (int s = 0; s < n_slices; ++s) { g += part[t][s]; u += part[kDualCap + t][s]; }
+        g = __bfloat162float(__float2bfloat16(g));
+        u = __bfloat162float(__float2bfloat16(u));
+        if (limit_g > 0.f) g = fminf(fmaxf(g, -limit_g), limit_g);
+        if (limit_u > 0.f) u = fminf(fmaxf(u, -limit_u), limit_u);
+        ag.y[r_begin + t] = __float2bfloat16((g / (1.0f + expf(-g))) * u);
+    }
+}
+
 // Any alignment, any stride: one warp per row, byte loads, FP32 FMA.  Only taken when a base pointer
 // or a row stride is not a multiple of 16 bytes.
 template <class Fmt, class Sc>
@@ -207,6 +269,30 @@ inline cudaError_t dense_launch(const DenseArgs& a, cudaStream_t stream) {
     cfg.attrs = attr;
     cfg.numAttrs = dense_pdl_enabled() ? 1 : 0;
     return cudaLaunchKernelEx(&cfg, dense_gemv_kernel<Fmt, Sc>, a);
+}
+
+// The gate / up pair: ag and au describe the two matrices (same K, N, x); the activation goes to ag.y.
+// Needs 16-byte aligned x, weights and row strides (returns cudaErrorInvalidValue otherwise).
+template <class Fmt, class Sc>
+inline cudaError_t dense_dual_launch(const DenseArgs& ag, const DenseArgs& au, float limit_g, float limit_u,
+                                     cudaStream_t stream) {
+    auto mis = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) != 0; };
+    if (mis(ag.x) || mis(ag.w) || mis(au.w) || (ag.w_stride & 15) != 0 || (au.w_stride & 15) != 0)
+        return cudaErrorInvalidValue;
+    long long grid = 2LL * dense_sm_count();
+    const long long need = ((long long)ag.N + kDualCap - 1) / kDualCap;
+    if (grid < need) grid = need;
+    if (grid > ag.N) grid = ag.N;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)grid);
+    cfg.blockDim = dim3(kDenseThreads);
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = dense_pdl_enabled() ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, dense_dual_swiglu_kernel<Fmt, Sc>, ag, au, limit_g, limit_u);
 }
 
 }  // namespace dsv4

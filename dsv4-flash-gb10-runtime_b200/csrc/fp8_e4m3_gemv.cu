@@ -65,3 +65,48 @@ DSV4_API int fp8_e4m3_gemv_m1_f32scale(const __nv_bfloat16* x, const uint8_t* W_
     }
     return 0;
 }
+
+// Additive: the shared expert's gated FFN for one token, all FP8 (what the reference composes from three
+// fp8_e4m3_gemv_m1 calls and an activation kernel: kernel/cpp-engine-mxfp4/dsv4_engine_mxfp4_wire.cu:523-556;
+// Python twin runtime/dsv4_engine_mxfp4.py:399-410):
+//   g = bf16(W1 x), u = bf16(W3 x), act = bf16(silu(clamp(g, limit_gate)) * clamp(u, limit_up)), out = bf16(W2 act).
+// W1, W3 [hidden, K_in], W2 [out_dim, hidden] E4M3 bytes with E8M0 128x128 tile scales, rows dense (stride = row
+// length).  limit_gate / limit_up <= 0 switch that clamp off: the C++ engine clamps the gate only (10, 0), the Python
+// engine both (10, 10).  Two launches chained by programmatic dependent launch; `workspace` holds the activation:
+// fp8_e4m3_shared_swiglu_workspace_bytes(hidden) bytes, 16-byte aligned.
+// Returns 0, -1 (K_in, hidden or out_dim not a multiple of 128 or > 16384), -8 (null / misaligned pointer),
+// -4 (launch failure).
+DSV4_API size_t fp8_e4m3_shared_swiglu_workspace_bytes(int hidden) {
+    return hidden > 0 ? (size_t)hidden * sizeof(__nv_bfloat16) : 0;
+}
+
+DSV4_API int fp8_e4m3_shared_swiglu_m1(const __nv_bfloat16* x, const uint8_t* W1_fp8, const uint8_t* W1_scale,
+                                       const uint8_t* W3_fp8, const uint8_t* W3_scale, const uint8_t* W2_fp8,
+                                       const uint8_t* W2_scale, int K_in, int hidden, int out_dim, float limit_gate,
+                                       float limit_up, __nv_bfloat16* out, void* workspace, cudaStream_t stream) {
+    auto bad = [](int v) { return v <= 0 || v % 128 != 0 || v > 16384; };
+    if (bad(K_in) || bad(hidden) || bad(out_dim)) {
+        std::fprintf(stderr, "fp8_e4m3_shared_swiglu_m1: unsupported shape K_in=%d hidden=%d out_dim=%d\n", K_in, hidden,
+                     out_dim);
+        return -1;
+    }
+    auto mis = [](const void* p) { return p == nullptr || (reinterpret_cast<uintptr_t>(p) & 15u) != 0; };
+    if (mis(x) || mis(W1_fp8) || mis(W3_fp8) || mis(W2_fp8) || !W1_scale || !W3_scale || !W2_scale || !out ||
+        mis(workspace)) {
+        std::fprintf(stderr, "fp8_e4m3_shared_swiglu_m1: null pointer or a tensor that is not 16-byte aligned\n");
+        return -8;
+    }
+    __nv_bfloat16* act = reinterpret_cast<__nv_bfloat16*>(workspace);
+    DenseArgs g, u, d;
+    g.x = x; g.w = W1_fp8; g.s = W1_scale; g.K = K_in; g.N = hidden; g.w_stride = K_in; g.s_stride = K_in / 128; g.y = act;
+    u = g; u.w = W3_fp8; u.s = W3_scale;
+    d.x = act; d.w = W2_fp8; d.s = W2_scale; d.K = hidden; d.N = out_dim; d.w_stride = hidden; d.s_stride = hidden / 128;
+    d.y = out;
+    cudaError_t err = dense_dual_launch<Fp8Format, Fp8Scale>(g, u, limit_gate, limit_up, stream);
+    if (err == cudaSuccess) err = dense_launch<Fp8Format, Fp8Scale>(d, stream);
+    if (err != cudaSuccess) {
+        std::fprintf(stderr, "fp8_e4m3_shared_swiglu_m1 launch failed: %s\n", cudaGetErrorString(err));
+        return -4;
+    }
+    return 0;
+}

@@ -7,7 +7,7 @@ W_fp8 uint8 [N, K] (raw E4M3), W_scale uint8 [N/128, K/128] (E8M0, one per 128x1
 """
 from __future__ import annotations
 
-from ctypes import c_int, c_int64
+from ctypes import c_float, c_int, c_int64
 from typing import Optional
 
 import torch
@@ -67,4 +67,40 @@ def fp8_e4m3_gemv_f32scale(W_fp8: torch.Tensor, W_scale: torch.Tensor, x: torch.
     return _run("fp8_e4m3_gemv_m1_f32scale", torch.float32, W_fp8, W_scale, x, out, stream)
 
 
-__all__ = ["fp8_e4m3_gemv", "fp8_e4m3_gemv_f32scale", "FP8_BLOCK_TILE"]
+def fp8_shared_swiglu(shared: dict, x: torch.Tensor, limit_gate: float = 10.0, limit_up: float = 0.0,
+                      out: Optional[torch.Tensor] = None, workspace: Optional[torch.Tensor] = None,
+                      stream: Optional[torch.cuda.Stream] = None) -> torch.Tensor:
+    """The shared expert's gated FFN for one token (reference: three fp8 GEMVs and an activation kernel,
+    kernel/cpp-engine-mxfp4/dsv4_engine_mxfp4_wire.cu:523-556): out = W2 (silu(clamp(W1 x)) * clamp(W3 x)).
+
+    `shared`: w1, w3 uint8 [hidden, K] and w2 uint8 [out_dim, hidden] raw E4M3, w1s / w3s / w2s uint8 E8M0 tile scales
+    (what bank_loader.load_shared_expert_fp8 returns); x bfloat16 [K].  The defaults are the C++ engine's clamp (gate
+    only, 10); the Python engine clamps both (10, 10)."""
+    w1, w3, w2 = shared["w1"], shared["w3"], shared["w2"]
+    K, hidden, out_dim = x.numel(), w1.shape[0], w2.shape[0]
+    for name, t in (("w1", w1), ("w3", w3), ("w2", w2), ("w1s", shared["w1s"]), ("w3s", shared["w3s"]), ("w2s", shared["w2s"])):
+        _require(t.is_cuda and t.dtype == torch.uint8 and t.is_contiguous(), f"{name} must be a contiguous cuda uint8 tensor")
+    _require(x.is_cuda and x.dtype == torch.bfloat16 and x.dim() == 1 and x.is_contiguous(), "x must be a contiguous cuda bfloat16 [K]")
+    _require(tuple(w1.shape) == (hidden, K) and tuple(w3.shape) == (hidden, K) and tuple(w2.shape) == (out_dim, hidden),
+             "w1 / w3 must be [hidden, K] and w2 [out_dim, hidden]")
+    for name, t, rows, cols in (("w1s", shared["w1s"], hidden, K), ("w3s", shared["w3s"], hidden, K), ("w2s", shared["w2s"], out_dim, hidden)):
+        _require(tuple(t.shape) == (rows // FP8_BLOCK_TILE, cols // FP8_BLOCK_TILE), f"{name} must be [{rows}/128, {cols}/128]")
+    lib = _capi.load("fp8")
+    need = lib.fp8_e4m3_shared_swiglu_workspace_bytes(c_int(hidden))
+    if workspace is None:
+        workspace = torch.empty(need, dtype=torch.uint8, device=x.device)
+    _require(workspace.is_cuda and workspace.numel() * workspace.element_size() >= need, f"workspace needs {need} bytes")
+    if out is None:
+        out = torch.empty(out_dim, dtype=torch.bfloat16, device=x.device)
+    _require(tuple(out.shape) == (out_dim,) and out.dtype == torch.bfloat16 and out.is_cuda and out.is_contiguous(),
+             f"out must be a contiguous cuda bfloat16 [{out_dim}]")
+    rc = lib.fp8_e4m3_shared_swiglu_m1(_capi.ptr(x), _capi.ptr(w1), _capi.ptr(shared["w1s"]), _capi.ptr(w3),
+                                       _capi.ptr(shared["w3s"]), _capi.ptr(w2), _capi.ptr(shared["w2s"]), c_int(K),
+                                       c_int(hidden), c_int(out_dim), c_float(limit_gate), c_float(limit_up),
+                                       _capi.ptr(out), _capi.ptr(workspace), _capi.stream_ptr(x.device, stream))
+    if rc != 0:
+        raise RuntimeError(f"fp8_e4m3_shared_swiglu_m1 returned {rc}")
+    return out
+
+
+__all__ = ["fp8_e4m3_gemv", "fp8_e4m3_gemv_f32scale", "fp8_shared_swiglu", "FP8_BLOCK_TILE"]

@@ -123,6 +123,20 @@ int fp8_e4m3_gemv_m1_f32scale(const uint16_t* x, const uint8_t* W_fp8, const flo
                               int64_t weight_row_stride_bytes, int64_t scale_row_stride_bytes, uint16_t* y,
                               void* stream);
 
+/* Added: the shared expert's gated FFN for one token, all FP8 - what the reference composes from three
+ * fp8_e4m3_gemv_m1 calls and an activation kernel (kernel/cpp-engine-mxfp4/dsv4_engine_mxfp4_wire.cu:523-556; Python
+ * twin runtime/dsv4_engine_mxfp4.py:399-410): g = bf16(W1 x), u = bf16(W3 x),
+ * act = bf16(silu(clamp(g, limit_gate)) * clamp(u, limit_up)), out = bf16(W2 act).  W1, W3 [hidden, K_in], W2
+ * [out_dim, hidden] raw E4M3 with E8M0 128x128 tile scales, dense rows; a limit <= 0 switches that clamp off (the
+ * C++ engine uses (10, 0), the Python engine (10, 10)).  workspace: fp8_e4m3_shared_swiglu_workspace_bytes(hidden)
+ * bytes, 16-byte aligned like x and the weights.  Returns -1 bad shape (multiples of 128, <= 16384), -8 null or
+ * misaligned pointer, -4 launch failure. */
+size_t fp8_e4m3_shared_swiglu_workspace_bytes(int hidden);
+int fp8_e4m3_shared_swiglu_m1(const uint16_t* x, const uint8_t* W1_fp8, const uint8_t* W1_scale, const uint8_t* W3_fp8,
+                              const uint8_t* W3_scale, const uint8_t* W2_fp8, const uint8_t* W2_scale, int K_in,
+                              int hidden, int out_dim, float limit_gate, float limit_up, uint16_t* out, void* workspace,
+                              void* stream);
+
 /* ---- libmxfp4_moe.so (added; no counterpart: the reference runs one token at a time) ---------------------- */
 
 /* Routed-expert MoE layer for a batch of tokens on the tensor cores: out[t] = sum_j weights[t,j] * FFN_{ids[t,j]}(x[t]).

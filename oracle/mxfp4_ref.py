@@ -14,7 +14,7 @@ import torch
 __all__ = [
     "FP4_E2M1_VALUES", "unpack_fp4", "pack_fp4", "e8m0_to_f32", "e4m3_to_f32",
     "dequant_mxfp4", "dequant_fp8_block128", "bf16_round", "bf16_bits",
-    "mxfp4_gemv_ref", "fp8_gemv_ref", "grouped_gemv_ref", "moe_layer_ref",
+    "mxfp4_gemv_ref", "fp8_gemv_ref", "shared_swiglu_fp8_ref", "grouped_gemv_ref", "moe_layer_ref",
     "router_scores_sqrt_softplus", "topk_lowest_index", "route_sqrt_softplus",
     "route_softmax", "max_abs_rel", "cosine", "MXFP4_BLOCK", "FP8_TILE",
 ]
@@ -185,6 +185,25 @@ def _silu(v: np.ndarray) -> np.ndarray:
     v = v.astype(np.float32)
     with np.errstate(over="ignore"):      # exp(+large) -> inf -> v / inf = -0.0, the right limit
         return v / (1.0 + np.exp(-v, dtype=np.float32))
+
+
+def shared_swiglu_fp8_ref(x_bf16: torch.Tensor, shared: dict, limit_gate: float = 10.0, limit_up: float = 0.0) -> np.ndarray:
+    """The shared expert's FP8 gated FFN for one token, FP32 throughout:
+    out = W2 (silu(clamp(W1 x, +-limit_gate)) * clamp(W3 x, +-limit_up)), a limit <= 0 meaning no clamp.
+
+    Restates runtime/dsv4_engine_mxfp4.py:399-410 (clamps both, limit 10) and
+    kernel/cpp-engine-mxfp4/dsv4_engine_mxfp4_wire.cu:506-556 (clamps the gate only); both round every GEMV output
+    and the activation to bf16, the oracle keeps FP32 (the tolerance is stated against it).  `shared`: w1, w3
+    [hidden, K], w2 [O, hidden] raw E4M3 bytes, w1s / w3s / w2s E8M0 128x128 tile scales.  Returns float32 [O].
+    """
+    x = x_bf16.float().numpy()
+    g = _matvec(dequant_fp8_block128(shared["w1"], shared["w1s"], ff="zero"), x)
+    u = _matvec(dequant_fp8_block128(shared["w3"], shared["w3s"], ff="zero"), x)
+    if limit_gate > 0:
+        g = np.clip(g, -limit_gate, limit_gate)
+    if limit_up > 0:
+        u = np.clip(u, -limit_up, limit_up)
+    return _matvec(dequant_fp8_block128(shared["w2"], shared["w2s"], ff="zero"), (_silu(g) * u).astype(np.float32))
 
 
 def grouped_gemv_ref(x_bf16, w1p, w3p, w2p, w1s, w3s, w2s, r) -> np.ndarray:
