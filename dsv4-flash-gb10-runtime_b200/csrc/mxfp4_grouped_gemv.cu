@@ -352,19 +352,22 @@ static cudaError_t allow_smem(Kernel kernel, size_t bytes, int (&done)[64]) {
     return err;
 }
 
-// DSV4_B200_FUSED: "0" two chained kernels; "pdl" the single kernel launched with programmatic stream
-// serialisation and its own grid barrier; anything else the single kernel launched cooperatively.
+// DSV4_B200_FUSED: "0" two chained kernels; "coop" the single kernel launched cooperatively (the runtime guarantees
+// that its 148 CTAs are co-resident: for callers that run grouped calls on several streams of one device); anything
+// else, and the default, the single kernel launched with programmatic stream serialisation (the next layer's CTAs are
+// scheduled while this layer's exit; its own bounded grid barrier relies on no second grid of the kernel being in
+// flight on the device, which a single decode stream guarantees).
 static int fused_mode() {
     static int v = -1;
     if (v < 0) {
         const char* e = std::getenv("DSV4_B200_FUSED");
-        v = (e && e[0] == '0') ? 0 : ((e && e[0] == 'p') ? 2 : 1);
+        v = (e && e[0] == '0') ? 0 : ((e && e[0] == 'c') ? 1 : 2);
     }
     return v;
 }
 static bool fused_enabled() { return fused_mode() != 0; }
 
-// Single persistent kernel (decode_fused.cuh), launched cooperatively with one CTA per SM.
+// Single persistent kernel (decode_fused.cuh), one CTA per SM, launched as fused_mode() says.
 // Returns 1 when it cannot be used here (the caller then launches the two chained kernels).
 template <int KT, int HT>
 static int grouped_launch_fused(const GroupedArgs& a, cudaStream_t stream, int h_shift, const RouteArgs& rt) {

@@ -1,6 +1,6 @@
 """The decode layer under its three launch modes (environment switch read once per process, hence child processes):
-single cooperative kernel (default), the same kernel launched with programmatic stream serialisation, and the
-two-kernel chain.  Each child checks the layer against the CPU oracle and against a repeat call (bitwise)."""
+the single kernel launched with programmatic stream serialisation (default), the same kernel launched
+cooperatively, and the two-kernel chain.  Each child checks the layer against the CPU oracle and against a repeat call (bitwise)."""
 import os
 import subprocess
 import sys
