@@ -24,18 +24,23 @@ import torch
 import torch.distributed as dist
 
 
+def dispatch_mask(ids: torch.Tensor, experts_per_rank: int, world: int) -> torch.Tensor:
+    """bool [world, T]: which token goes to which rank (a token at most once per rank)."""
+    T = ids.shape[0]
+    dest = torch.div(ids.to(torch.int64), experts_per_rank, rounding_mode="floor")
+    mask = torch.zeros(T, world, dtype=torch.bool, device=ids.device)
+    mask.scatter_(1, dest.clamp_(0, world - 1), True)
+    return mask.t().contiguous()
+
+
 def plan_dispatch(ids: torch.Tensor, experts_per_rank: int, world: int):
     """Which token goes to which rank.
 
     Returns (token_of, send_counts): `token_of` lists token indices grouped by destination rank (ranks ascending,
     tokens ascending inside a rank, a token at most once per rank); `send_counts[r]` rows go to rank r.
     """
-    T = ids.shape[0]
-    dest = torch.div(ids.to(torch.int64), experts_per_rank, rounding_mode="floor")
-    mask = torch.zeros(T, world, dtype=torch.bool, device=ids.device)
-    mask.scatter_(1, dest.clamp_(0, world - 1), True)
-    pairs = mask.t().nonzero()                       # (rank, token), sorted by rank then token
-    return pairs[:, 1].contiguous(), mask.sum(dim=0)
+    mask = dispatch_mask(ids, experts_per_rank, world)
+    return mask.nonzero()[:, 1].contiguous(), mask.sum(dim=1)
 
 
 def _all_to_all_rows(rows: torch.Tensor, send_counts, recv_counts, group) -> torch.Tensor:
@@ -62,12 +67,17 @@ def ep_moe_forward(x: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor, n_
     T, k = ids.shape
     K = x.shape[1]
     O = K if out_dim is None else int(out_dim)
-    token_of, send_counts = plan_dispatch(ids, per, world)
-    counts_out = send_counts.to(torch.int64)
+    mask = dispatch_mask(ids, per, world)                             # [world, T]
+    counts_out = mask.sum(dim=1).to(torch.int64)
     counts_in = torch.empty(world, dtype=torch.int64, device=x.device)
     dist.all_to_all_single(counts_in, counts_out, group=group)
     both = torch.stack([counts_out, counts_in]).tolist()              # the layer's one host synchronisation
     send_l, recv_l = [int(c) for c in both[0]], [int(c) for c in both[1]]
+    # positions of the set entries of the mask in (rank, token) order; the count is known on the host by now, so no
+    # second synchronisation (a stable sort of the flags instead of nonzero())
+    flat = mask.reshape(-1)
+    order = torch.sort(flat.to(torch.uint8), descending=True, stable=True).indices[: sum(send_l)]
+    token_of = order % T
 
     # one payload row per (token, destination): activation | k ids | k weights, as bytes
     xb = x.contiguous().view(torch.uint8).view(T, -1)
@@ -103,4 +113,4 @@ def shard_bank(bank: Dict[str, torch.Tensor], rank: int, world: int) -> Dict[str
     return {name: t[rank * per:(rank + 1) * per].contiguous() for name, t in bank.items()}
 
 
-__all__ = ["plan_dispatch", "ep_moe_forward", "shard_bank"]
+__all__ = ["dispatch_mask", "plan_dispatch", "ep_moe_forward", "shard_bank"]
