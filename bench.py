@@ -237,33 +237,50 @@ def batched_configs(rt, qz, torch, dist, bank, dev, rank, world):
         def local_forward(rows, local_ids, wts):
             return rt.moe_forward(local_bank, rows, local_ids, wts)
 
+        equal = (hi - lo) * world == T                                 # every rank holds the same number of tokens
+
+        def step_a2a():
+            return ep.ep_moe_forward(x_l, ids_l, w_l, E, local_forward)
+
         def step():
             if world > 1:
-                return ep.ep_moe_forward(x_l, ids_l, w_l, E, local_forward)
+                if equal:
+                    return ep.ep_moe_forward_gathered(x_l, ids_l, w_l, E, local_forward)
+                return step_a2a()
             return rt.moe_forward(bank, x_l, ids_l, w_l)
+
+        def timed_ms(fn):
+            for _ in range(2):
+                fn()
+            if world > 1:
+                dist.barrier()
+            torch.cuda.synchronize()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            for _ in range(iters):
+                fn()
+            b.record()
+            torch.cuda.synchronize()
+            t_ms = a.elapsed_time(b) / iters
+            if world > 1:
+                t = torch.tensor([t_ms], device=dev, dtype=torch.float64)
+                dist.all_reduce(t, op=dist.ReduceOp.MAX)
+                t_ms = float(t.item())
+            return t_ms
 
         y = step()
         torch.cuda.synchronize()
         parity = None
-        if world > 1 and rank == 0:
+        if world > 1:
             ref = rt.moe_forward(bank, x_l, ids_l, w_l).float()
             parity = float((y.float() - ref).abs().max() / ref.abs().max())
-        for _ in range(2):
-            step()
-        if world > 1:
-            dist.barrier()
-        torch.cuda.synchronize()
-        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        a.record()
-        for _ in range(iters):
-            step()
-        b.record()
-        torch.cuda.synchronize()
-        ms = a.elapsed_time(b) / iters
-        if world > 1:
-            t = torch.tensor([ms], device=dev, dtype=torch.float64)
+            y2 = step_a2a()
+            parity = max(parity, float((y2.float() - ref).abs().max() / ref.abs().max()))
+            t = torch.tensor([parity], device=dev, dtype=torch.float64)
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
-            ms = float(t.item())
+            parity = float(t.item())
+        ms = timed_ms(step)
+        ms_a2a = timed_ms(step_a2a) if world > 1 and equal else None
         distinct = int(ids.unique().numel())
         flops = T * TOP_K * 2 * 3 * HIDDEN * EXPERT_FF
         min_bytes = distinct * BYTES_PER_EXPERT + 2 * T * HIDDEN * 2
@@ -272,7 +289,10 @@ def batched_configs(rt, qz, torch, dist, bank, dev, rank, world):
                      "frac_of_measured_hbm_peak": min_bytes / ms / 1e6 / world / measured_hbm_peak()[0],
                      "gbs_min_bytes": min_bytes / ms / 1e6, "distinct_experts": distinct,
                      "max_abs_vs_1gpu_over_inf_norm": parity,
-                     "exchange": "none" if world == 1 else "torch.distributed all_to_all_single (NCCL): rows out, rows back"}
+                     "exchange": "none" if world == 1 else
+                     ("all_gather of the tokens + reduce_scatter of the partial rows (NCCL), no host synchronisation"
+                      if equal else "all_to_all_single (NCCL): one row per (token, owner rank) out, partial rows back"),
+                     "ms_all_to_all_variant": ms_a2a}
     if rt.moe_device_status() != 0:
         raise RuntimeError("a batched kernel gave up on a bounded wait")
     return out

@@ -106,6 +106,47 @@ def ep_moe_forward(x: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor, n_
     return acc.to(x.dtype)
 
 
+def ep_moe_forward_gathered(x: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor, n_experts: int,
+                            local_forward: Callable[[torch.Tensor, torch.Tensor, torch.Tensor], torch.Tensor],
+                            group: Optional[dist.ProcessGroup] = None, out_dim: Optional[int] = None) -> torch.Tensor:
+    """The same layer for the case that EVERY rank holds the same number of tokens T, without any data-dependent
+    shape: all-gather of the tokens (activation, ids, weights), every rank runs its own experts over all world * T
+    tokens with the ids of other ranks masked (-1), and a reduce-scatter (FP32 sum) brings every token's partial
+    rows home.  No host synchronisation, no sorting or gathering, two collectives whose sizes do not depend on the
+    routing (so the whole layer can be captured in a CUDA graph); the price is wire volume (every token visits
+    every rank) and that the summation order over ranks is the collective's (fixed for a given communicator, but
+    not "rank order" as in ep_moe_forward).  On a backend without reduce-scatter (gloo) an all-reduce is used.
+    """
+    world = dist.get_world_size(group)
+    rank = dist.get_rank(group)
+    if n_experts % world:
+        raise ValueError(f"{n_experts} experts do not split over {world} ranks")
+    per = n_experts // world
+    T, k = ids.shape
+    K = x.shape[1]
+    O = K if out_dim is None else int(out_dim)
+    xg = torch.empty(world * T, K, dtype=x.dtype, device=x.device)
+    ig = torch.empty(world * T, k, dtype=torch.int32, device=x.device)
+    wg = torch.empty(world * T, k, dtype=torch.float32, device=x.device)
+    for dst, src in ((xg, x), (ig, ids.to(torch.int32)), (wg, weights.to(torch.float32))):
+        try:
+            dist.all_gather_into_tensor(dst, src.contiguous(), group=group)
+        except (RuntimeError, NotImplementedError):
+            parts = [torch.empty_like(src) for _ in range(world)]
+            dist.all_gather(parts, src.contiguous(), group=group)
+            dst.copy_(torch.cat(parts, dim=0))
+    local = ig - rank * per
+    local = torch.where((local >= 0) & (local < per), local, torch.full_like(local, -1))
+    y = local_forward(xg, local, wg).float()                          # [world * T, O]; zero rows where nothing is local
+    out = torch.empty(T, O, dtype=torch.float32, device=x.device)
+    try:
+        dist.reduce_scatter_tensor(out, y, op=dist.ReduceOp.SUM, group=group)
+    except (RuntimeError, NotImplementedError):
+        dist.all_reduce(y, op=dist.ReduceOp.SUM, group=group)
+        out = y[rank * T:(rank + 1) * T]
+    return out.to(x.dtype)
+
+
 def shard_bank(bank: Dict[str, torch.Tensor], rank: int, world: int) -> Dict[str, torch.Tensor]:
     """This rank's contiguous range of experts of a bank stacked over all experts."""
     n = bank["w1p"].shape[0]
@@ -113,4 +154,4 @@ def shard_bank(bank: Dict[str, torch.Tensor], rank: int, world: int) -> Dict[str
     return {name: t[rank * per:(rank + 1) * per].contiguous() for name, t in bank.items()}
 
 
-__all__ = ["dispatch_mask", "plan_dispatch", "ep_moe_forward", "shard_bank"]
+__all__ = ["dispatch_mask", "plan_dispatch", "ep_moe_forward", "ep_moe_forward_gathered", "shard_bank"]

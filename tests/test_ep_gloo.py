@@ -58,6 +58,15 @@ def _worker(rank, world, port, T, E, k, K):
     for r in range(world):
         want += _fake_layer(x, ids, w, r * per, (r + 1) * per).float()
     ok = torch.equal(out, want.to(torch.bfloat16))
+
+    # the all-gather / reduce-scatter formulation (every rank sees every token; rows without a local expert are
+    # all -1 and must come back as zeros); the sum over ranks is the collective's, so allow one bf16 ulp
+    def local_forward_all(rows, local_ids, wts):
+        gids = torch.where(local_ids >= 0, local_ids + rank * per, torch.full_like(local_ids, -1))
+        return _fake_layer(rows, gids, wts, rank * per, (rank + 1) * per)
+
+    out2 = ep.ep_moe_forward_gathered(x, ids, w, E, local_forward_all)
+    ok = ok and bool(((out2.float() - want).abs() <= 2.0 ** -7 * want.abs() + 1e-6).all())
     flag = torch.tensor([1 if ok else 0])
     dist.all_reduce(flag, op=dist.ReduceOp.MIN)
     dist.destroy_process_group()
