@@ -242,10 +242,15 @@ def batched_configs(rt, qz, torch, dist, bank, dev, rank, world):
         def step_a2a():
             return ep.ep_moe_forward(x_l, ids_l, w_l, E, local_forward)
 
+        def step_gathered():
+            return ep.ep_moe_forward_gathered(x_l, ids_l, w_l, E, local_forward)
+
+        peer_ctx = ep.PeerCombine(hi - lo, HIDDEN, dev) if world > 1 and equal else None
+
         def step():
             if world > 1:
-                if equal:
-                    return ep.ep_moe_forward_gathered(x_l, ids_l, w_l, E, local_forward)
+                if equal:          # combine fused with peer stores into the home rank's buffer
+                    return ep.ep_moe_forward_peer(peer_ctx, x_l, ids_l, w_l, E, local_bank)
                 return step_a2a()
             return rt.moe_forward(bank, x_l, ids_l, w_l)
 
@@ -274,13 +279,15 @@ def batched_configs(rt, qz, torch, dist, bank, dev, rank, world):
         if world > 1:
             ref = rt.moe_forward(bank, x_l, ids_l, w_l).float()
             parity = float((y.float() - ref).abs().max() / ref.abs().max())
-            y2 = step_a2a()
-            parity = max(parity, float((y2.float() - ref).abs().max() / ref.abs().max()))
+            for other in ([step_a2a, step_gathered] if equal else []):
+                y2 = other()
+                parity = max(parity, float((y2.float() - ref).abs().max() / ref.abs().max()))
             t = torch.tensor([parity], device=dev, dtype=torch.float64)
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
             parity = float(t.item())
         ms = timed_ms(step)
         ms_a2a = timed_ms(step_a2a) if world > 1 and equal else None
+        ms_gathered = timed_ms(step_gathered) if world > 1 and equal else None
         distinct = int(ids.unique().numel())
         flops = T * TOP_K * 2 * 3 * HIDDEN * EXPERT_FF
         min_bytes = distinct * BYTES_PER_EXPERT + 2 * T * HIDDEN * 2
@@ -290,9 +297,10 @@ def batched_configs(rt, qz, torch, dist, bank, dev, rank, world):
                      "gbs_min_bytes": min_bytes / ms / 1e6, "distinct_experts": distinct,
                      "max_abs_vs_1gpu_over_inf_norm": parity,
                      "exchange": "none" if world == 1 else
-                     ("all_gather of the tokens + reduce_scatter of the partial rows (NCCL), no host synchronisation"
+                     ("all_gather of the tokens (NCCL); partial rows stored by the layer's combine kernel straight into the "
+                      "home rank's buffer (peer memory over NVLink), one barrier, rank-order sum; no host synchronisation"
                       if equal else "all_to_all_single (NCCL): one row per (token, owner rank) out, partial rows back"),
-                     "ms_all_to_all_variant": ms_a2a}
+                     "ms_gather_reduce_scatter_variant": ms_gathered, "ms_all_to_all_variant": ms_a2a}
     if rt.moe_device_status() != 0:
         raise RuntimeError("a batched kernel gave up on a bounded wait")
     return out

@@ -122,7 +122,8 @@ static int moe_forward_impl(int path, const __nv_bfloat16* x, const uint8_t* ban
                                const uint8_t* bank_W2_packed, const uint8_t* bank_W1_scale,
                                const uint8_t* bank_W3_scale, const uint8_t* bank_W2_scale, const int* ids,
                                const float* weights, int n_tokens, int n_experts, int K_in, int hidden, int out_dim,
-                               int k, __nv_bfloat16* out, void* workspace, cudaStream_t stream) {
+                               int k, __nv_bfloat16* out, void* workspace, cudaStream_t stream,
+                               const MoePeerOut* peer = nullptr) {
     const char* who = "mxfp4_moe_forward";
     if (path != 0 && path != 1) return -1;
     if (n_tokens < 0 || k <= 0 || n_experts <= 0 || n_experts > kMoeMaxExperts || K_in <= 0 || K_in % 256 != 0 ||
@@ -133,9 +134,9 @@ static int moe_forward_impl(int path, const __nv_bfloat16* x, const uint8_t* ban
     }
     if (n_tokens == 0) return 0;
     if (!x || !bank_W1_packed || !bank_W3_packed || !bank_W2_packed || !bank_W1_scale || !bank_W3_scale ||
-        !bank_W2_scale || !ids || !weights || !out || !workspace || !aligned16(x) || !aligned16(bank_W1_packed) ||
+        !bank_W2_scale || !ids || !weights || (!out && !peer) || !workspace || !aligned16(x) || !aligned16(bank_W1_packed) ||
         !aligned16(bank_W3_packed) || !aligned16(bank_W2_packed) || !aligned16(bank_W1_scale) ||
-        !aligned16(bank_W3_scale) || !aligned16(bank_W2_scale) || !aligned16(workspace) || !aligned16(out)) {
+        !aligned16(bank_W3_scale) || !aligned16(bank_W2_scale) || !aligned16(workspace) || (out && !aligned16(out))) {
         std::fprintf(stderr, "%s: null pointer or a tensor that is not 16-byte aligned\n", who);
         return -2;
     }
@@ -191,7 +192,10 @@ static int moe_forward_impl(int path, const __nv_bfloat16* x, const uint8_t* ban
         if (qerr == cudaSuccess) {
             launch_k(moe_gemm_mxf4_kernel<1>, dim3(grid), dim3(kGemmThreads), MoeQGemmLayout<1>::kBytes, stream, qd);
             dim3 cgrid((out_dim / 4 + 127) / 128, n_tokens);
-            launch_k(moe_combine_kernel, dim3(cgrid), dim3(128), 0, stream, y, g.pair_slot, n_tokens, k, out_dim, out);
+            if (peer)
+                launch_k(moe_combine_peer_kernel, dim3(cgrid), dim3(128), 0, stream, y, g.pair_slot, n_tokens, k, out_dim, *peer);
+            else
+                launch_k(moe_combine_kernel, dim3(cgrid), dim3(128), 0, stream, y, g.pair_slot, n_tokens, k, out_dim, out);
             qerr = cudaGetLastError();
         }
         if (qerr != cudaSuccess) {
@@ -226,7 +230,10 @@ static int moe_forward_impl(int path, const __nv_bfloat16* x, const uint8_t* ban
     }
     if (err == cudaSuccess) {
         dim3 cgrid((out_dim / 4 + 127) / 128, n_tokens);
-        launch_k(moe_combine_kernel, dim3(cgrid), dim3(128), 0, stream, y, g.pair_slot, n_tokens, k, out_dim, out);
+        if (peer)
+            launch_k(moe_combine_peer_kernel, dim3(cgrid), dim3(128), 0, stream, y, g.pair_slot, n_tokens, k, out_dim, *peer);
+        else
+            launch_k(moe_combine_kernel, dim3(cgrid), dim3(128), 0, stream, y, g.pair_slot, n_tokens, k, out_dim, out);
         err = cudaGetLastError();
     }
     if (err != cudaSuccess) {
@@ -272,4 +279,56 @@ DSV4_API int mxfp4_moe_device_status(void) {
     if (cudaMemcpyFromSymbol(&v, g_device_status, sizeof(int)) != cudaSuccess) return -1;
     if (v != 0) cudaMemcpyToSymbol(g_device_status, &zero, sizeof(int));
     return v;
+}
+
+// Expert parallel, combine fused with the exchange: the layer of mxfp4_moe_forward over the GATHERED batch of
+// world * tokens_per_rank tokens (token t belongs to rank t / tokens_per_rank; ids index this rank's local bank, -1
+// where the expert lives elsewhere), whose per-token sums are not written to a local output but stored by the
+// combine kernel straight into the receive buffer of the token's home rank - peer memory, plain stores over NVLink,
+// the transfer being the kernel's own epilogue.  recv_ptrs: HOST array of `world` device pointers, entry r the
+// receive buffer of rank r, bf16 [world][tokens_per_rank][out_dim] (peer-mapped, e.g. symmetric memory); this rank
+// writes slice [my_rank] of each.  After a barrier over the ranks every rank calls mxfp4_moe_ep_sum on its own
+// buffer.  Return codes as mxfp4_moe_forward; -1 also for world outside 1..16 or a token count that is not
+// world * tokens_per_rank.
+DSV4_API int mxfp4_moe_forward_ep(const __nv_bfloat16* x, const uint8_t* bank_W1_packed, const uint8_t* bank_W3_packed,
+                                  const uint8_t* bank_W2_packed, const uint8_t* bank_W1_scale,
+                                  const uint8_t* bank_W3_scale, const uint8_t* bank_W2_scale, const int* ids,
+                                  const float* weights, int n_tokens, int n_experts, int K_in, int hidden, int out_dim,
+                                  int k, void* const* recv_ptrs, int world, int my_rank, int tokens_per_rank,
+                                  void* workspace, cudaStream_t stream) {
+    if (world < 1 || world > kMoeMaxRanks || my_rank < 0 || my_rank >= world || tokens_per_rank <= 0 ||
+        n_tokens != world * tokens_per_rank || !recv_ptrs) {
+        std::fprintf(stderr, "mxfp4_moe_forward_ep: bad rank layout world=%d rank=%d tokens_per_rank=%d n_tokens=%d\n", world,
+                     my_rank, tokens_per_rank, n_tokens);
+        return -1;
+    }
+    MoePeerOut peer = {};
+    for (int r = 0; r < world; ++r) {
+        if (!recv_ptrs[r] || !aligned16(recv_ptrs[r])) return -2;
+        peer.recv[r] = reinterpret_cast<__nv_bfloat16*>(recv_ptrs[r]);
+    }
+    peer.world = world; peer.my_rank = my_rank; peer.tokens_per_rank = tokens_per_rank;
+    static int path = -1;
+    if (path < 0) {
+        const char* e = std::getenv("DSV4_B200_MOE_PATH");
+        path = (e && e[0] == 'f') ? 0 : 1;
+    }
+    return moe_forward_impl(path, x, bank_W1_packed, bank_W3_packed, bank_W2_packed, bank_W1_scale, bank_W3_scale,
+                            bank_W2_scale, ids, weights, n_tokens, n_experts, K_in, hidden, out_dim, k, nullptr,
+                            workspace, stream, &peer);
+}
+
+// out[t] = bf16(sum over ranks r = 0 .. world-1, in that order, of recv[r][t]): the home rank's side of
+// mxfp4_moe_forward_ep, after the barrier.  recv bf16 [world][n_tokens][out_dim], out bf16 [n_tokens][out_dim];
+// out_dim a multiple of 4.  Returns 0, -1 bad shape, -2 null / misaligned pointer, -3 launch failure.
+DSV4_API int mxfp4_moe_ep_sum(const __nv_bfloat16* recv, int world, int n_tokens, int out_dim, __nv_bfloat16* out,
+                              cudaStream_t stream) {
+    if (world < 1 || n_tokens < 0 || out_dim <= 0 || out_dim % 4 != 0) return -1;
+    if (n_tokens == 0) return 0;
+    if (!recv || !out || !aligned16(recv) || !aligned16(out)) return -2;
+    const long long n4 = (long long)n_tokens * out_dim / 4;
+    long long grid = (n4 + 255) / 256;
+    if (grid > 8LL * sm_count()) grid = 8LL * sm_count();
+    launch_k(moe_ep_sum_kernel, dim3((unsigned)grid), dim3(256), 0, stream, recv, world, n_tokens, out_dim, out);
+    return cudaGetLastError() == cudaSuccess ? 0 : -3;
 }

@@ -171,6 +171,60 @@ __global__ void moe_combine_kernel(const float* __restrict__ y, const int* __res
     *reinterpret_cast<uint2*>(out + (size_t)t * O + o) = packed;
 }
 
+// Expert parallel: where the per-token sums of a rank go.  Token t of the gathered batch belongs to rank
+// t / tokens_per_rank; its partial row is stored straight into THAT rank's receive buffer (a peer pointer: plain
+// stores over NVLink, no collective), at [my_rank][t % tokens_per_rank][O].
+constexpr int kMoeMaxRanks = 16;
+struct MoePeerOut {
+    __nv_bfloat16* recv[kMoeMaxRanks];     // receive buffer of every rank, [world][tokens_per_rank][O] bf16
+    int world, my_rank, tokens_per_rank;
+};
+
+// moe_combine_kernel with the peer destination above: the exchange is the kernel's own stores, row by row.
+__global__ void moe_combine_peer_kernel(const float* __restrict__ y, const int* __restrict__ pair_slot, int n_tokens,
+                                        int k, int O, const MoePeerOut peer) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int t = blockIdx.y;
+    const int o = (blockIdx.x * blockDim.x + threadIdx.x) * 4;
+    if (t >= n_tokens || o >= O) return;
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int j = 0; j < k; ++j) {
+        const int slot = pair_slot[t * k + j];
+        if (slot < 0) continue;
+        const float4 v = __ldcs(reinterpret_cast<const float4*>(y + (size_t)slot * O + o));
+        acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+    }
+    __nv_bfloat162 lo = __floats2bfloat162_rn(acc.x, acc.y), hi = __floats2bfloat162_rn(acc.z, acc.w);
+    uint2 packed;
+    packed.x = *reinterpret_cast<uint32_t*>(&lo);
+    packed.y = *reinterpret_cast<uint32_t*>(&hi);
+    const int home = t / peer.tokens_per_rank, tl = t - home * peer.tokens_per_rank;
+    __nv_bfloat16* dst = peer.recv[home] + ((size_t)peer.my_rank * peer.tokens_per_rank + tl) * O + o;
+    *reinterpret_cast<uint2*>(dst) = packed;
+}
+
+// out[t, :] = bf16( sum_r recv[r][t, :] ), ranks in ascending order (fixed summation order).
+__global__ void moe_ep_sum_kernel(const __nv_bfloat16* __restrict__ recv, int world, int n_tokens, int O,
+                                  __nv_bfloat16* __restrict__ out) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const size_t n4 = (size_t)n_tokens * O / 4;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n4; i += (size_t)gridDim.x * blockDim.x) {
+        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+        for (int r = 0; r < world; ++r) {
+            const uint2 q = __ldcs(reinterpret_cast<const uint2*>(recv + (size_t)r * n_tokens * O) + i);
+            acc.x += __uint_as_float(q.x << 16); acc.y += __uint_as_float(q.x & 0xffff0000u);
+            acc.z += __uint_as_float(q.y << 16); acc.w += __uint_as_float(q.y & 0xffff0000u);
+        }
+        __nv_bfloat162 lo = __floats2bfloat162_rn(acc.x, acc.y), hi = __floats2bfloat162_rn(acc.z, acc.w);
+        uint2 packed;
+        packed.x = *reinterpret_cast<uint32_t*>(&lo);
+        packed.y = *reinterpret_cast<uint32_t*>(&hi);
+        reinterpret_cast<uint2*>(out)[i] = packed;
+    }
+}
+
 // Rows of activations -> three MXFP4 terms whose sum reproduces the row to ~12 bits:
 //   v ~ q1 * 2^e1 + q2 * 2^e2 + q3 * 2^e3   per 32-element block, q E2M1, 2^e the smallest power of two with
 // amax(what is left) <= 6 * 2^e (no saturation),

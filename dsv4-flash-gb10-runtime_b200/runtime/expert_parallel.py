@@ -147,6 +147,81 @@ def ep_moe_forward_gathered(x: torch.Tensor, ids: torch.Tensor, weights: torch.T
     return out.to(x.dtype)
 
 
+class PeerCombine:
+    """Receive buffers in symmetric memory for ep_moe_forward_peer: two buffers of bf16 [world, T, O] per rank
+    (alternating between calls, so one barrier per call suffices), mapped on every rank of the group."""
+
+    def __init__(self, tokens_per_rank: int, out_dim: int, device, group: Optional[dist.ProcessGroup] = None):
+        import torch.distributed._symmetric_memory as symm_mem
+        group = group or dist.group.WORLD
+        self.world, self.rank = dist.get_world_size(group), dist.get_rank(group)
+        self.T, self.O = int(tokens_per_rank), int(out_dim)
+        self.slab = self.world * self.T * self.O
+        self.buf = symm_mem.empty(2 * self.slab, dtype=torch.bfloat16, device=device)
+        self.handle = symm_mem.rendezvous(self.buf, group)
+        self.calls = 0
+        import ctypes
+        self._ptr_arrays = []
+        for half in range(2):
+            arr = (ctypes.c_void_p * self.world)()
+            for r in range(self.world):
+                arr[r] = int(self.handle.buffer_ptrs[r]) + half * self.slab * 2
+            self._ptr_arrays.append(arr)
+
+    def next_half(self) -> int:
+        half = self.calls & 1
+        self.calls += 1
+        return half
+
+
+def ep_moe_forward_peer(ctx: PeerCombine, x: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor, n_experts: int,
+                        local_bank: Dict[str, torch.Tensor], group: Optional[dist.ProcessGroup] = None) -> torch.Tensor:
+    """ep_moe_forward_gathered with the return path fused into the layer: after the all-gather of the tokens every
+    rank runs its experts over all tokens, and the layer's combine kernel stores each token's partial row straight
+    into the home rank's receive buffer (peer memory over NVLink: the exchange is the kernel's epilogue, there is no
+    reduce-scatter); one barrier over the ranks, then every rank adds the `world` partial rows of its tokens in rank
+    order (deterministic).  Every rank must hold ctx.T tokens.  No host synchronisation."""
+    from ctypes import c_int
+    from . import _capi
+    from .moe_batched import forward_workspace_bytes
+    lib = _capi.load("moe")
+    world, rank = ctx.world, ctx.rank
+    per = n_experts // world
+    T, k = ids.shape
+    K = x.shape[1]
+    if T != ctx.T or n_experts % world:
+        raise ValueError("ep_moe_forward_peer: every rank must hold ctx.T tokens and the experts must split evenly")
+    xg = torch.empty(world * T, K, dtype=x.dtype, device=x.device)
+    ig = torch.empty(world * T, k, dtype=torch.int32, device=x.device)
+    wg = torch.empty(world * T, k, dtype=torch.float32, device=x.device)
+    dist.all_gather_into_tensor(xg, x.contiguous(), group=group)
+    dist.all_gather_into_tensor(ig, ids.to(torch.int32).contiguous(), group=group)
+    dist.all_gather_into_tensor(wg, weights.to(torch.float32).contiguous(), group=group)
+    local = ig - rank * per
+    local = torch.where((local >= 0) & (local < per), local, torch.full_like(local, -1)).contiguous()
+    E_local, hidden, out_dim = local_bank["w1p"].shape[0], local_bank["w1p"].shape[1], local_bank["w2p"].shape[1]
+    if out_dim != ctx.O:
+        raise ValueError("ep_moe_forward_peer: out_dim differs from the context's")
+    ws = torch.empty(forward_workspace_bytes(world * T, k, K, hidden, out_dim, E_local), dtype=torch.uint8, device=x.device)
+    half = ctx.next_half()
+    rc = lib.mxfp4_moe_forward_ep(_capi.ptr(xg), _capi.ptr(local_bank["w1p"]), _capi.ptr(local_bank["w3p"]),
+                                  _capi.ptr(local_bank["w2p"]), _capi.ptr(local_bank["w1s"]), _capi.ptr(local_bank["w3s"]),
+                                  _capi.ptr(local_bank["w2s"]), _capi.ptr(local), _capi.ptr(wg), c_int(world * T),
+                                  c_int(E_local), c_int(K), c_int(hidden), c_int(out_dim), c_int(k),
+                                  ctx._ptr_arrays[half], c_int(world), c_int(rank), c_int(T), _capi.ptr(ws),
+                                  _capi.stream_ptr(x.device))
+    if rc != 0:
+        raise RuntimeError(f"mxfp4_moe_forward_ep returned {rc}")
+    ctx.handle.barrier()                                             # every rank's partial rows have landed
+    out = torch.empty(T, out_dim, dtype=torch.bfloat16, device=x.device)
+    mine = ctx.buf[half * ctx.slab:(half + 1) * ctx.slab]
+    rc = lib.mxfp4_moe_ep_sum(_capi.ptr(mine), c_int(world), c_int(T), c_int(out_dim), _capi.ptr(out),
+                              _capi.stream_ptr(x.device))
+    if rc != 0:
+        raise RuntimeError(f"mxfp4_moe_ep_sum returned {rc}")
+    return out
+
+
 def shard_bank(bank: Dict[str, torch.Tensor], rank: int, world: int) -> Dict[str, torch.Tensor]:
     """This rank's contiguous range of experts of a bank stacked over all experts."""
     n = bank["w1p"].shape[0]
@@ -154,4 +229,5 @@ def shard_bank(bank: Dict[str, torch.Tensor], rank: int, world: int) -> Dict[str
     return {name: t[rank * per:(rank + 1) * per].contiguous() for name, t in bank.items()}
 
 
-__all__ = ["dispatch_mask", "plan_dispatch", "ep_moe_forward", "ep_moe_forward_gathered", "shard_bank"]
+__all__ = ["dispatch_mask", "plan_dispatch", "ep_moe_forward", "ep_moe_forward_gathered", "PeerCombine",
+           "ep_moe_forward_peer", "shard_bank"]

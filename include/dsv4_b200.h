@@ -161,6 +161,21 @@ size_t mxfp4_moe_forward_workspace_bytes(int n_tokens, int k, int K_in, int hidd
  * out); clears it.  Synchronises the device. */
 int mxfp4_moe_device_status(void);
 
+/* Expert parallel with the combine fused into the exchange: mxfp4_moe_forward over the gathered batch of
+ * world * tokens_per_rank tokens (token t belongs to rank t / tokens_per_rank; ids index this rank's local bank, -1
+ * where the expert lives on another rank); the combine kernel stores every token's partial row straight into the
+ * receive buffer of its home rank (peer memory, plain stores over NVLink).  recv_ptrs: HOST array of `world` device
+ * pointers, entry r = rank r's receive buffer, bf16 [world][tokens_per_rank][out_dim], mapped on this device.  After a
+ * barrier over the ranks each rank calls mxfp4_moe_ep_sum on its own buffer.  Return codes as mxfp4_moe_forward. */
+int mxfp4_moe_forward_ep(const uint16_t* x, const uint8_t* bank_W1_packed, const uint8_t* bank_W3_packed,
+                         const uint8_t* bank_W2_packed, const uint8_t* bank_W1_scale, const uint8_t* bank_W3_scale,
+                         const uint8_t* bank_W2_scale, const int* ids, const float* weights, int n_tokens, int n_experts,
+                         int K_in, int hidden, int out_dim, int k, void* const* recv_ptrs, int world, int my_rank,
+                         int tokens_per_rank, void* workspace, void* stream);
+
+/* out[t] = bf16(sum of recv[r][t] over ranks r = 0 .. world-1, in that order).  recv bf16 [world][n_tokens][out_dim]. */
+int mxfp4_moe_ep_sum(const uint16_t* recv, int world, int n_tokens, int out_dim, uint16_t* out, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -1,5 +1,5 @@
-"""Expert parallel on real GPUs (NCCL, two ranks, one process per GPU): both formulations against the single-GPU
-layer on the same tokens.  Skipped on a box with fewer than two GPUs."""
+"""Expert parallel on real GPUs (NCCL, two ranks, one process per GPU): the three formulations (all-to-all, all-gather +
+reduce-scatter, all-gather + combine fused with peer stores) against the single-GPU layer on the same tokens.  Skipped on a box with fewer than two GPUs."""
 import os
 import socket
 import subprocess
@@ -38,6 +38,13 @@ for name, fn in (("all_to_all", ep.ep_moe_forward), ("gathered", ep.ep_moe_forwa
     out = fn(x, ids, w, E, fwd).float()
     err = float((out - ref).abs().max() / ref.abs().max())
     assert err <= 1e-2, (name, err)
+ctx = ep.PeerCombine(T, K, dev)
+for rep in range(3):                                      # alternating receive buffers, one barrier per call
+    out = ep.ep_moe_forward_peer(ctx, x, ids, w, E, local_bank).float()
+    err = float((out - ref).abs().max() / ref.abs().max())
+    assert err <= 1e-2, ("peer", rep, err)
+    again = ep.ep_moe_forward_peer(ctx, x, ids, w, E, local_bank)
+    assert torch.equal(again.view(torch.int16), out.to(torch.bfloat16).view(torch.int16))
 torch.cuda.synchronize()
 assert rt.moe_device_status() == 0
 dist.barrier()
