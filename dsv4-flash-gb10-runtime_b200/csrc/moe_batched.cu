@@ -318,17 +318,22 @@ DSV4_API int mxfp4_moe_forward_ep(const __nv_bfloat16* x, const uint8_t* bank_W1
                             workspace, stream, &peer);
 }
 
-// out[t] = bf16(sum over ranks r = 0 .. world-1, in that order, of recv[r][t]): the home rank's side of
-// mxfp4_moe_forward_ep, after the barrier.  recv bf16 [world][n_tokens][out_dim], out bf16 [n_tokens][out_dim];
-// out_dim a multiple of 4.  Returns 0, -1 bad shape, -2 null / misaligned pointer, -3 launch failure.
-DSV4_API int mxfp4_moe_ep_sum(const __nv_bfloat16* recv, int world, int n_tokens, int out_dim, __nv_bfloat16* out,
-                              cudaStream_t stream) {
-    if (world < 1 || n_tokens < 0 || out_dim <= 0 || out_dim % 4 != 0) return -1;
+// out[t] = bf16(sum of recv[r][t] over the ranks r that own one of token t's experts, in ascending order): the home
+// rank's side of mxfp4_moe_forward_ep, after the barrier.  recv bf16 [world][n_tokens][out_dim]; ids int32
+// [n_tokens, k] GLOBAL expert ids of this rank's tokens (a rank owns experts [r, r + 1) * experts_per_rank; ranks
+// without an expert of the token stored nothing and are skipped); out bf16 [n_tokens][out_dim]; out_dim a multiple
+// of 4, world <= 16.  Returns 0, -1 bad shape, -2 null / misaligned pointer, -3 launch failure.
+DSV4_API int mxfp4_moe_ep_sum(const __nv_bfloat16* recv, const int* ids, int k, int experts_per_rank, int world,
+                              int n_tokens, int out_dim, __nv_bfloat16* out, cudaStream_t stream) {
+    if (world < 1 || world > kMoeMaxRanks || n_tokens < 0 || out_dim <= 0 || out_dim % 4 != 0 || k <= 0 ||
+        experts_per_rank <= 0)
+        return -1;
     if (n_tokens == 0) return 0;
-    if (!recv || !out || !aligned16(recv) || !aligned16(out)) return -2;
+    if (!recv || !ids || !out || !aligned16(recv) || !aligned16(out)) return -2;
     const long long n4 = (long long)n_tokens * out_dim / 4;
     long long grid = (n4 + 255) / 256;
     if (grid > 8LL * sm_count()) grid = 8LL * sm_count();
-    launch_k(moe_ep_sum_kernel, dim3((unsigned)grid), dim3(256), 0, stream, recv, world, n_tokens, out_dim, out);
+    launch_k(moe_ep_sum_kernel, dim3((unsigned)grid), dim3(256), 0, stream, recv, ids, k, experts_per_rank, world,
+             n_tokens, out_dim, out);
     return cudaGetLastError() == cudaSuccess ? 0 : -3;
 }

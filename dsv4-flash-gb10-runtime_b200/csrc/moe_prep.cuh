@@ -189,12 +189,15 @@ __global__ void moe_combine_peer_kernel(const float* __restrict__ y, const int* 
     const int o = (blockIdx.x * blockDim.x + threadIdx.x) * 4;
     if (t >= n_tokens || o >= O) return;
     float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    bool any = false;
     for (int j = 0; j < k; ++j) {
         const int slot = pair_slot[t * k + j];
         if (slot < 0) continue;
+        any = true;
         const float4 v = __ldcs(reinterpret_cast<const float4*>(y + (size_t)slot * O + o));
         acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
     }
+    if (!any) return;                       // none of the token's experts lives here: the home rank skips this slice
     __nv_bfloat162 lo = __floats2bfloat162_rn(acc.x, acc.y), hi = __floats2bfloat162_rn(acc.z, acc.w);
     uint2 packed;
     packed.x = *reinterpret_cast<uint32_t*>(&lo);
@@ -204,15 +207,25 @@ __global__ void moe_combine_peer_kernel(const float* __restrict__ y, const int* 
     *reinterpret_cast<uint2*>(dst) = packed;
 }
 
-// out[t, :] = bf16( sum_r recv[r][t, :] ), ranks in ascending order (fixed summation order).
-__global__ void moe_ep_sum_kernel(const __nv_bfloat16* __restrict__ recv, int world, int n_tokens, int O,
+// out[t, :] = bf16( sum_r recv[r][t, :] ), ranks in ascending order (fixed summation order), over the ranks that
+// own at least one of the token's experts (ids [n_tokens, k] global, experts_per_rank per rank): the others wrote
+// nothing.
+__global__ void moe_ep_sum_kernel(const __nv_bfloat16* __restrict__ recv, const int* __restrict__ ids, int k,
+                                  int experts_per_rank, int world, int n_tokens, int O,
                                   __nv_bfloat16* __restrict__ out) {
     pdl_launch_dependents();
     pdl_wait();
     const size_t n4 = (size_t)n_tokens * O / 4;
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n4; i += (size_t)gridDim.x * blockDim.x) {
+        const int t = (int)(i / (size_t)(O / 4));
+        uint32_t owners = 0;
+        for (int j = 0; j < k; ++j) {
+            const int e = ids[t * k + j];
+            if (e >= 0 && e / experts_per_rank < world) owners |= 1u << (e / experts_per_rank);
+        }
         float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
         for (int r = 0; r < world; ++r) {
+            if (!((owners >> r) & 1u)) continue;
             const uint2 q = __ldcs(reinterpret_cast<const uint2*>(recv + (size_t)r * n_tokens * O) + i);
             acc.x += __uint_as_float(q.x << 16); acc.y += __uint_as_float(q.x & 0xffff0000u);
             acc.z += __uint_as_float(q.y << 16); acc.w += __uint_as_float(q.y & 0xffff0000u);

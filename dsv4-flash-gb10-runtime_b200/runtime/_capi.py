@@ -31,7 +31,7 @@ SIGNATURES = {
         "mxfp4_moe_forward_path": (c_int, [c_int] + [_P] * 9 + [c_int] * 6 + [_P, _P, _P]),
         "mxfp4_moe_forward_workspace_bytes": (c_size_t, [c_int] * 6),
         "mxfp4_moe_forward_ep": (c_int, [_P] * 9 + [c_int] * 6 + [_P] + [c_int] * 3 + [_P, _P]),
-        "mxfp4_moe_ep_sum": (c_int, [_P, c_int, c_int, c_int, _P, _P]),
+        "mxfp4_moe_ep_sum": (c_int, [_P, _P, c_int, c_int, c_int, c_int, c_int, _P, _P]),
         "mxfp4_moe_device_status": (c_int, []),
     },
     "fp8": {

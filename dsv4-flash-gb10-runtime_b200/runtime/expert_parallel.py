@@ -192,11 +192,14 @@ def ep_moe_forward_peer(ctx: PeerCombine, x: torch.Tensor, ids: torch.Tensor, we
     if T != ctx.T or n_experts % world:
         raise ValueError("ep_moe_forward_peer: every rank must hold ctx.T tokens and the experts must split evenly")
     xg = torch.empty(world * T, K, dtype=x.dtype, device=x.device)
-    ig = torch.empty(world * T, k, dtype=torch.int32, device=x.device)
-    wg = torch.empty(world * T, k, dtype=torch.float32, device=x.device)
     dist.all_gather_into_tensor(xg, x.contiguous(), group=group)
-    dist.all_gather_into_tensor(ig, ids.to(torch.int32).contiguous(), group=group)
-    dist.all_gather_into_tensor(wg, weights.to(torch.float32).contiguous(), group=group)
+    # ids and weights travel together (one collective): [T, 2k] 32-bit words per rank
+    ids32 = ids.to(torch.int32).contiguous()
+    meta = torch.cat([ids32, weights.to(torch.float32).contiguous().view(torch.int32)], dim=1)
+    mg = torch.empty(world * T, 2 * k, dtype=torch.int32, device=x.device)
+    dist.all_gather_into_tensor(mg, meta, group=group)
+    ig = mg[:, :k]
+    wg = mg[:, k:].contiguous().view(torch.float32)
     local = ig - rank * per
     local = torch.where((local >= 0) & (local < per), local, torch.full_like(local, -1)).contiguous()
     E_local, hidden, out_dim = local_bank["w1p"].shape[0], local_bank["w1p"].shape[1], local_bank["w2p"].shape[1]
@@ -215,8 +218,8 @@ def ep_moe_forward_peer(ctx: PeerCombine, x: torch.Tensor, ids: torch.Tensor, we
     ctx.handle.barrier()                                             # every rank's partial rows have landed
     out = torch.empty(T, out_dim, dtype=torch.bfloat16, device=x.device)
     mine = ctx.buf[half * ctx.slab:(half + 1) * ctx.slab]
-    rc = lib.mxfp4_moe_ep_sum(_capi.ptr(mine), c_int(world), c_int(T), c_int(out_dim), _capi.ptr(out),
-                              _capi.stream_ptr(x.device))
+    rc = lib.mxfp4_moe_ep_sum(_capi.ptr(mine), _capi.ptr(ids32), c_int(k), c_int(per), c_int(world), c_int(T),
+                              c_int(out_dim), _capi.ptr(out), _capi.stream_ptr(x.device))
     if rc != 0:
         raise RuntimeError(f"mxfp4_moe_ep_sum returned {rc}")
     return out

@@ -173,8 +173,11 @@ int mxfp4_moe_forward_ep(const uint16_t* x, const uint8_t* bank_W1_packed, const
                          int K_in, int hidden, int out_dim, int k, void* const* recv_ptrs, int world, int my_rank,
                          int tokens_per_rank, void* workspace, void* stream);
 
-/* out[t] = bf16(sum of recv[r][t] over ranks r = 0 .. world-1, in that order).  recv bf16 [world][n_tokens][out_dim]. */
-int mxfp4_moe_ep_sum(const uint16_t* recv, int world, int n_tokens, int out_dim, uint16_t* out, void* stream);
+/* out[t] = bf16(sum of recv[r][t] over the ranks r that own one of token t's experts, ascending r).  recv bf16
+ * [world][n_tokens][out_dim]; ids int32 [n_tokens, k] global expert ids of this rank's tokens; rank r owns experts
+ * [r, r + 1) * experts_per_rank (the other ranks stored nothing for the token and are skipped). */
+int mxfp4_moe_ep_sum(const uint16_t* recv, const int* ids, int k, int experts_per_rank, int world, int n_tokens,
+                     int out_dim, uint16_t* out, void* stream);
 
 #ifdef __cplusplus
 }
