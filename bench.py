@@ -249,12 +249,15 @@ def batched_configs(rt, qz, torch, dist, bank, dev, rank, world):
         def step_gathered():
             return ep.ep_moe_forward_gathered(x_l, ids_l, w_l, E, local_forward)
 
-        peer_ctx = ep.PeerCombine(hi - lo, HIDDEN, dev) if world > 1 and equal else None
+        peer_ctx = ep.PeerCombine(hi - lo, HIDDEN, dev, in_dim=HIDDEN, k=TOP_K) if world > 1 and equal else None
+
+        def step_peer_combine():      # NCCL all-gather in, combine fused with peer stores out
+            return ep.ep_moe_forward_peer(peer_ctx, x_l, ids_l, w_l, E, local_bank)
 
         def step():
             if world > 1:
-                if equal:          # combine fused with peer stores into the home rank's buffer
-                    return ep.ep_moe_forward_peer(peer_ctx, x_l, ids_l, w_l, E, local_bank)
+                if equal:          # both sides over peer memory: tokens read from the publishing rank, partial rows
+                    return ep.ep_moe_forward_peer_inputs(peer_ctx, x_l, ids_l, w_l, E, local_bank)   # stored at home
                 return step_a2a()
             return rt.moe_forward(bank, x_l, ids_l, w_l)
 
@@ -283,7 +286,7 @@ def batched_configs(rt, qz, torch, dist, bank, dev, rank, world):
         if world > 1:
             ref = rt.moe_forward(bank, x_l, ids_l, w_l).float()
             parity = float((y.float() - ref).abs().max() / ref.abs().max())
-            for other in ([step_a2a, step_gathered] if equal else []):
+            for other in ([step_a2a, step_gathered, step_peer_combine] if equal else []):
                 y2 = other()
                 parity = max(parity, float((y2.float() - ref).abs().max() / ref.abs().max()))
             t = torch.tensor([parity], device=dev, dtype=torch.float64)
@@ -292,6 +295,7 @@ def batched_configs(rt, qz, torch, dist, bank, dev, rank, world):
         ms = timed_ms(step)
         ms_a2a = timed_ms(step_a2a) if world > 1 and equal else None
         ms_gathered = timed_ms(step_gathered) if world > 1 and equal else None
+        ms_peer_combine = timed_ms(step_peer_combine) if world > 1 and equal else None
         distinct = int(ids.unique().numel())
         flops = T * TOP_K * 2 * 3 * HIDDEN * EXPERT_FF
         min_bytes = distinct * BYTES_PER_EXPERT + 2 * T * HIDDEN * 2
@@ -301,9 +305,11 @@ def batched_configs(rt, qz, torch, dist, bank, dev, rank, world):
                      "gbs_min_bytes": min_bytes / ms / 1e6, "distinct_experts": distinct,
                      "max_abs_vs_1gpu_over_inf_norm": parity,
                      "exchange": "none" if world == 1 else
-                     ("all_gather of the tokens (NCCL); partial rows stored by the layer's combine kernel straight into the "
-                      "home rank's buffer (peer memory over NVLink), one barrier, rank-order sum; no host synchronisation"
+                     ("peer memory over NVLink on both sides (symmetric memory, no collective library): tokens read by the "
+                      "layer's kernels from the rank that published them, partial rows stored by its combine kernel "
+                      "into the home rank's buffer, two barriers, rank-order sum; no host synchronisation"
                       if equal else "all_to_all_single (NCCL): one row per (token, owner rank) out, partial rows back"),
+                     "ms_all_gather_then_peer_combine_variant": ms_peer_combine,
                      "ms_gather_reduce_scatter_variant": ms_gathered, "ms_all_to_all_variant": ms_a2a}
     if rt.moe_device_status() != 0:
         raise RuntimeError("a batched kernel gave up on a bounded wait")

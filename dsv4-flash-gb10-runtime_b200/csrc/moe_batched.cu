@@ -123,7 +123,7 @@ static int moe_forward_impl(int path, const __nv_bfloat16* x, const uint8_t* ban
                                const uint8_t* bank_W3_scale, const uint8_t* bank_W2_scale, const int* ids,
                                const float* weights, int n_tokens, int n_experts, int K_in, int hidden, int out_dim,
                                int k, __nv_bfloat16* out, void* workspace, cudaStream_t stream,
-                               const MoePeerOut* peer = nullptr) {
+                               const MoePeerOut* peer = nullptr, const MoePeerIn* peer_in = nullptr) {
     const char* who = "mxfp4_moe_forward";
     if (path != 0 && path != 1) return -1;
     if (n_tokens < 0 || k <= 0 || n_experts <= 0 || n_experts > kMoeMaxExperts || K_in <= 0 || K_in % 256 != 0 ||
@@ -133,8 +133,8 @@ static int moe_forward_impl(int path, const __nv_bfloat16* x, const uint8_t* ban
         return -1;
     }
     if (n_tokens == 0) return 0;
-    if (!x || !bank_W1_packed || !bank_W3_packed || !bank_W2_packed || !bank_W1_scale || !bank_W3_scale ||
-        !bank_W2_scale || !ids || !weights || (!out && !peer) || !workspace || !aligned16(x) || !aligned16(bank_W1_packed) ||
+    if ((!x && !peer_in) || !bank_W1_packed || !bank_W3_packed || !bank_W2_packed || !bank_W1_scale || !bank_W3_scale ||
+        !bank_W2_scale || !ids || !weights || (!out && !peer) || !workspace || (x && !aligned16(x)) || !aligned16(bank_W1_packed) ||
         !aligned16(bank_W3_packed) || !aligned16(bank_W2_packed) || !aligned16(bank_W1_scale) ||
         !aligned16(bank_W3_scale) || !aligned16(bank_W2_scale) || !aligned16(workspace) || (out && !aligned16(out))) {
         std::fprintf(stderr, "%s: null pointer or a tensor that is not 16-byte aligned\n", who);
@@ -172,7 +172,12 @@ static int moe_forward_impl(int path, const __nv_bfloat16* x, const uint8_t* ban
         uint8_t* mq = ws + m.mq; uint8_t* ms = ws + m.ms;
         float* midf = reinterpret_cast<float*>(ws + m.midf);
         const int qgrid = 4 * grid;
-        launch_k(moe_quantize_mxfp4x3_kernel<__nv_bfloat16>, dim3(qgrid), dim3(256), 0, stream, x, n_tokens, K_in, xq, xs);
+        if (peer_in)
+            launch_k(moe_quantize_mxfp4x3_kernel<__nv_bfloat16, true>, dim3(qgrid), dim3(256), 0, stream, x,
+                     (long long)n_tokens, K_in, xq, xs, *peer_in);
+        else
+            launch_k(moe_quantize_mxfp4x3_kernel<__nv_bfloat16, false>, dim3(qgrid), dim3(256), 0, stream, x,
+                     (long long)n_tokens, K_in, xq, xs, MoePeerIn{});
         MoeQGemmArgs qu;
         qu.wa_p = bank_W1_packed; qu.wb_p = bank_W3_packed; qu.wa_s = bank_W1_scale; qu.wb_s = bank_W3_scale;
         qu.stride_p = (long long)hidden * (K_in / 2); qu.stride_s = (long long)hidden * (K_in / 32);
@@ -181,7 +186,8 @@ static int moe_forward_impl(int path, const __nv_bfloat16* x, const uint8_t* ban
         cudaError_t qerr = allow_smem(moe_gemm_mxf4_kernel<0>, MoeQGemmLayout<0>::kBytes, qup_done);
         if (qerr == cudaSuccess) {
             launch_k(moe_gemm_mxf4_kernel<0>, dim3(grid), dim3(kGemmThreads), MoeQGemmLayout<0>::kBytes, stream, qu);
-            launch_k(moe_quantize_mxfp4x3_kernel<float>, dim3(qgrid), dim3(256), 0, stream, midf, (long long)P, hidden, mq, ms);
+            launch_k(moe_quantize_mxfp4x3_kernel<float, false>, dim3(qgrid), dim3(256), 0, stream, midf, (long long)P,
+                     hidden, mq, ms, MoePeerIn{});
             qerr = cudaGetLastError();
         }
         MoeQGemmArgs qd = qu;
@@ -336,4 +342,58 @@ DSV4_API int mxfp4_moe_ep_sum(const __nv_bfloat16* recv, const int* ids, int k, 
     launch_k(moe_ep_sum_kernel, dim3((unsigned)grid), dim3(256), 0, stream, recv, ids, k, experts_per_rank, world,
              n_tokens, out_dim, out);
     return cudaGetLastError() == cudaSuccess ? 0 : -3;
+}
+
+// Expert parallel with BOTH sides over peer memory (no collective library on the path): every rank publishes its
+// tokens in buffers that are mapped on all ranks (symmetric memory): x bf16 [tokens_per_rank, K_in], ids int32
+// [tokens_per_rank, k] (global expert ids), weights FP32 [tokens_per_rank, k].  After a barrier over the ranks this
+// call runs the rank's experts over the whole batch of world * tokens_per_rank tokens: a small kernel turns the
+// published ids into this rank's view (local index, -1 for experts of other ranks), the activation quantiser reads
+// every token's row from the rank that published it (plain loads over NVLink), and the combine kernel stores the
+// partial rows into the home ranks' receive buffers as in mxfp4_moe_forward_ep.  x_ptrs / ids_ptrs / w_ptrs /
+// recv_ptrs: HOST arrays of `world` device pointers.  Block-scaled tensor-core path only.  workspace:
+// mxfp4_moe_forward_ep2_workspace_bytes.  Return codes as mxfp4_moe_forward_ep.
+DSV4_API size_t mxfp4_moe_forward_ep2_workspace_bytes(int world, int tokens_per_rank, int k, int K_in, int hidden,
+                                                      int out_dim, int n_experts_local) {
+    if (world <= 0 || tokens_per_rank <= 0 || k <= 0) return 0;
+    const long long T = (long long)world * tokens_per_rank;
+    const size_t base = map_workspace(T, k, K_in, hidden, out_dim, n_experts_local).total;
+    return base + 2 * (((size_t)T * k * 4 + 255) & ~size_t(255));
+}
+
+DSV4_API int mxfp4_moe_forward_ep2(void* const* x_ptrs, void* const* ids_ptrs, void* const* w_ptrs,
+                                   const uint8_t* bank_W1_packed, const uint8_t* bank_W3_packed,
+                                   const uint8_t* bank_W2_packed, const uint8_t* bank_W1_scale,
+                                   const uint8_t* bank_W3_scale, const uint8_t* bank_W2_scale, int tokens_per_rank,
+                                   int n_experts_local, int K_in, int hidden, int out_dim, int k,
+                                   void* const* recv_ptrs, int world, int my_rank, void* workspace,
+                                   cudaStream_t stream) {
+    if (world < 1 || world > kMoeMaxRanks || my_rank < 0 || my_rank >= world || tokens_per_rank <= 0 || k <= 0 ||
+        n_experts_local <= 0 || !x_ptrs || !ids_ptrs || !w_ptrs || !recv_ptrs || !workspace) {
+        std::fprintf(stderr, "mxfp4_moe_forward_ep2: bad rank layout or null table\n");
+        return -1;
+    }
+    MoePeerIn in = {};
+    MoePeerOut peer = {};
+    for (int r = 0; r < world; ++r) {
+        if (!x_ptrs[r] || !ids_ptrs[r] || !w_ptrs[r] || !recv_ptrs[r] || !aligned16(x_ptrs[r]) || !aligned16(recv_ptrs[r]))
+            return -2;
+        in.x[r] = reinterpret_cast<const __nv_bfloat16*>(x_ptrs[r]);
+        in.ids[r] = reinterpret_cast<const int*>(ids_ptrs[r]);
+        in.w[r] = reinterpret_cast<const float*>(w_ptrs[r]);
+        peer.recv[r] = reinterpret_cast<__nv_bfloat16*>(recv_ptrs[r]);
+    }
+    in.world = peer.world = world; in.my_rank = peer.my_rank = my_rank;
+    in.tokens_per_rank = peer.tokens_per_rank = tokens_per_rank; in.experts_per_rank = n_experts_local;
+    const int n_tokens = world * tokens_per_rank;
+    uint8_t* ws = reinterpret_cast<uint8_t*>(workspace);
+    const size_t base = map_workspace(n_tokens, k, K_in, hidden, out_dim, n_experts_local).total;
+    int* ids_local = reinterpret_cast<int*>(ws + base);
+    float* w_local = reinterpret_cast<float*>(ws + base + (((size_t)n_tokens * k * 4 + 255) & ~size_t(255)));
+    const int n_meta = n_tokens * k;
+    launch_k(moe_ep_gather_meta_kernel, dim3((unsigned)((n_meta + 255) / 256)), dim3(256), 0, stream, in, k, ids_local,
+             w_local);
+    return moe_forward_impl(1, nullptr, bank_W1_packed, bank_W3_packed, bank_W2_packed, bank_W1_scale, bank_W3_scale,
+                            bank_W2_scale, ids_local, w_local, n_tokens, n_experts_local, K_in, hidden, out_dim, k,
+                            nullptr, workspace, stream, &peer, &in);
 }

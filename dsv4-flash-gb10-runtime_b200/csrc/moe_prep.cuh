@@ -180,6 +180,31 @@ struct MoePeerOut {
     int world, my_rank, tokens_per_rank;
 };
 
+// Expert parallel, input side: the tokens of the gathered batch are not copied together first; rank r's tokens
+// are read where they are, from the buffers rank r published (peer pointers: plain loads over NVLink).
+struct MoePeerIn {
+    const __nv_bfloat16* x[kMoeMaxRanks];      // [tokens_per_rank, K] bf16 of every rank
+    const int* ids[kMoeMaxRanks];              // [tokens_per_rank, k] GLOBAL expert ids
+    const float* w[kMoeMaxRanks];              // [tokens_per_rank, k] router weights
+    int world, my_rank, tokens_per_rank, experts_per_rank;
+};
+
+// ids / weights of all ranks -> this rank's view of the gathered batch: local expert index, or -1 where the
+// expert lives on another rank (a pair the layer skips).
+__global__ void moe_ep_gather_meta_kernel(const MoePeerIn in, int k, int* __restrict__ ids_local,
+                                          float* __restrict__ w_local) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int per_rank = in.tokens_per_rank * k;
+    const int n = in.world * per_rank;
+    for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gridDim.x * blockDim.x) {
+        const int r = i / per_rank, j = i - r * per_rank;
+        const int e = __ldcg(in.ids[r] + j) - in.my_rank * in.experts_per_rank;
+        ids_local[i] = (e >= 0 && e < in.experts_per_rank) ? e : -1;
+        w_local[i] = __ldcg(in.w[r] + j);
+    }
+}
+
 // moe_combine_kernel with the peer destination above: the exchange is the kernel's own stores, row by row.
 __global__ void moe_combine_peer_kernel(const float* __restrict__ y, const int* __restrict__ pair_slot, int n_tokens,
                                         int k, int O, const MoePeerOut peer) {
@@ -246,9 +271,11 @@ __global__ void moe_ep_sum_kernel(const __nv_bfloat16* __restrict__ recv, const 
 // Output: q [3][rows][K / 2] packed (low nibble = even element), s [3][rows][K / 32] E8M0 bytes.
 // A lane owns eight neighbouring elements, four lanes own a block, a warp 256 consecutive elements of a row
 // (K must be a multiple of 256): 16- or 32-byte loads, one 4-byte store per lane and term.
-template <class Elem>
+// With PEER the rows are not in `src` but in the per-rank buffers of `in` (row t = row t % tokens_per_rank of rank
+// t / tokens_per_rank).
+template <class Elem, bool PEER = false>
 __global__ void moe_quantize_mxfp4x3_kernel(const Elem* __restrict__ src, long long rows, int K,
-                                            uint8_t* __restrict__ q, uint8_t* __restrict__ s) {
+                                            uint8_t* __restrict__ q, uint8_t* __restrict__ s, const MoePeerIn in = {}) {
     pdl_launch_dependents();
     pdl_wait();
     const int lane = threadIdx.x & 31;
@@ -259,7 +286,13 @@ __global__ void moe_quantize_mxfp4x3_kernel(const Elem* __restrict__ src, long l
         const long long e0 = w * 256 + 8 * lane;                    // first of this lane's eight elements (row-major)
         float v[8];
         if constexpr (sizeof(Elem) == 2) {
-            const uint4 u = __ldcs(reinterpret_cast<const uint4*>(src + e0));
+            const Elem* from = src + e0;
+            if constexpr (PEER) {
+                const long long row = e0 / K;
+                const int r = (int)(row / in.tokens_per_rank);
+                from = reinterpret_cast<const Elem*>(in.x[r]) + (row - (long long)r * in.tokens_per_rank) * K + (e0 - row * K);
+            }
+            const uint4 u = __ldcs(reinterpret_cast<const uint4*>(from));
             const uint32_t uu[4] = {u.x, u.y, u.z, u.w};
 #pragma unroll
             for (int i = 0; i < 4; ++i) {

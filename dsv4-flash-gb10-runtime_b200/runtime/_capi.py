@@ -32,6 +32,8 @@ SIGNATURES = {
         "mxfp4_moe_forward_workspace_bytes": (c_size_t, [c_int] * 6),
         "mxfp4_moe_forward_ep": (c_int, [_P] * 9 + [c_int] * 6 + [_P] + [c_int] * 3 + [_P, _P]),
         "mxfp4_moe_ep_sum": (c_int, [_P, _P, c_int, c_int, c_int, c_int, c_int, _P, _P]),
+        "mxfp4_moe_forward_ep2_workspace_bytes": (c_size_t, [c_int] * 7),
+        "mxfp4_moe_forward_ep2": (c_int, [_P] * 9 + [c_int] * 6 + [_P] + [c_int] * 2 + [_P, _P]),
         "mxfp4_moe_device_status": (c_int, []),
     },
     "fp8": {

@@ -151,11 +151,31 @@ class PeerCombine:
     """Receive buffers in symmetric memory for ep_moe_forward_peer: two buffers of bf16 [world, T, O] per rank
     (alternating between calls, so one barrier per call suffices), mapped on every rank of the group."""
 
-    def __init__(self, tokens_per_rank: int, out_dim: int, device, group: Optional[dist.ProcessGroup] = None):
+    def __init__(self, tokens_per_rank: int, out_dim: int, device, group: Optional[dist.ProcessGroup] = None,
+                 in_dim: Optional[int] = None, k: Optional[int] = None):
+        """With in_dim (K) and k given, the context also holds this rank's PUBLISHED inputs in symmetric memory
+        (x bf16 [T, K], ids int32 [T, k], weights float32 [T, k]) for ep_moe_forward_peer_inputs."""
         import torch.distributed._symmetric_memory as symm_mem
         group = group or dist.group.WORLD
         self.world, self.rank = dist.get_world_size(group), dist.get_rank(group)
         self.T, self.O = int(tokens_per_rank), int(out_dim)
+        self.K, self.k = in_dim, k
+        if in_dim is not None and k is not None:
+            import ctypes as _ct
+            nx, nm = self.T * in_dim * 2, self.T * k * 4
+            nx_al = (nx + 255) & ~255
+            nm_al = (nm + 255) & ~255
+            self.pub = symm_mem.empty(nx_al + 2 * nm_al, dtype=torch.uint8, device=device)
+            self.pub_handle = symm_mem.rendezvous(self.pub, group)
+            self.pub_x = self.pub[:nx].view(torch.bfloat16).view(self.T, in_dim)
+            self.pub_ids = self.pub[nx_al:nx_al + nm].view(torch.int32).view(self.T, k)
+            self.pub_w = self.pub[nx_al + nm_al:nx_al + nm_al + nm].view(torch.float32).view(self.T, k)
+            self._x_ptrs = (_ct.c_void_p * self.world)()
+            self._ids_ptrs = (_ct.c_void_p * self.world)()
+            self._w_ptrs = (_ct.c_void_p * self.world)()
+            for r in range(self.world):
+                base = int(self.pub_handle.buffer_ptrs[r])
+                self._x_ptrs[r], self._ids_ptrs[r], self._w_ptrs[r] = base, base + nx_al, base + nx_al + nm_al
         self.slab = self.world * self.T * self.O
         self.buf = symm_mem.empty(2 * self.slab, dtype=torch.bfloat16, device=device)
         self.handle = symm_mem.rendezvous(self.buf, group)
@@ -225,6 +245,50 @@ def ep_moe_forward_peer(ctx: PeerCombine, x: torch.Tensor, ids: torch.Tensor, we
     return out
 
 
+def ep_moe_forward_peer_inputs(ctx: PeerCombine, x: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor,
+                               n_experts: int, local_bank: Dict[str, torch.Tensor]) -> torch.Tensor:
+    """ep_moe_forward_peer without any collective library on the path: every rank copies its tokens (activations,
+    ids, weights) into its published symmetric-memory buffers; after a barrier every rank runs its experts over the
+    whole batch, READING each token from the rank that published it (the quantiser and a small id kernel load over
+    NVLink) and storing each partial row into the home rank's receive buffer; a second barrier, then the rank-order
+    sum.  The context must have been built with in_dim and k.  Block-scaled tensor-core path only."""
+    from ctypes import c_int
+    from . import _capi
+    lib = _capi.load("moe")
+    world, rank = ctx.world, ctx.rank
+    per = n_experts // world
+    T, k = ids.shape
+    K = x.shape[1]
+    if ctx.K != K or ctx.k != k or T != ctx.T or n_experts % world:
+        raise ValueError("ep_moe_forward_peer_inputs: shapes differ from the context's")
+    E_local, hidden, out_dim = local_bank["w1p"].shape[0], local_bank["w1p"].shape[1], local_bank["w2p"].shape[1]
+    if out_dim != ctx.O or E_local != per:
+        raise ValueError("ep_moe_forward_peer_inputs: bank does not match the context")
+    ctx.pub_x.copy_(x)
+    ctx.pub_ids.copy_(ids)
+    ctx.pub_w.copy_(weights)
+    ctx.handle.barrier()                                             # every rank's tokens are published
+    ws = torch.empty(lib.mxfp4_moe_forward_ep2_workspace_bytes(c_int(world), c_int(T), c_int(k), c_int(K), c_int(hidden),
+                                                               c_int(out_dim), c_int(E_local)),
+                     dtype=torch.uint8, device=x.device)
+    half = ctx.next_half()
+    rc = lib.mxfp4_moe_forward_ep2(ctx._x_ptrs, ctx._ids_ptrs, ctx._w_ptrs, _capi.ptr(local_bank["w1p"]),
+                                   _capi.ptr(local_bank["w3p"]), _capi.ptr(local_bank["w2p"]), _capi.ptr(local_bank["w1s"]),
+                                   _capi.ptr(local_bank["w3s"]), _capi.ptr(local_bank["w2s"]), c_int(T), c_int(E_local),
+                                   c_int(K), c_int(hidden), c_int(out_dim), c_int(k), ctx._ptr_arrays[half], c_int(world),
+                                   c_int(rank), _capi.ptr(ws), _capi.stream_ptr(x.device))
+    if rc != 0:
+        raise RuntimeError(f"mxfp4_moe_forward_ep2 returned {rc}")
+    ctx.handle.barrier()                                             # every rank's partial rows have landed
+    out = torch.empty(T, out_dim, dtype=torch.bfloat16, device=x.device)
+    mine = ctx.buf[half * ctx.slab:(half + 1) * ctx.slab]
+    rc = lib.mxfp4_moe_ep_sum(_capi.ptr(mine), _capi.ptr(ctx.pub_ids), c_int(k), c_int(per), c_int(world), c_int(T),
+                              c_int(out_dim), _capi.ptr(out), _capi.stream_ptr(x.device))
+    if rc != 0:
+        raise RuntimeError(f"mxfp4_moe_ep_sum returned {rc}")
+    return out
+
+
 def shard_bank(bank: Dict[str, torch.Tensor], rank: int, world: int) -> Dict[str, torch.Tensor]:
     """This rank's contiguous range of experts of a bank stacked over all experts."""
     n = bank["w1p"].shape[0]
@@ -233,4 +297,4 @@ def shard_bank(bank: Dict[str, torch.Tensor], rank: int, world: int) -> Dict[str
 
 
 __all__ = ["dispatch_mask", "plan_dispatch", "ep_moe_forward", "ep_moe_forward_gathered", "PeerCombine",
-           "ep_moe_forward_peer", "shard_bank"]
+           "ep_moe_forward_peer", "ep_moe_forward_peer_inputs", "shard_bank"]

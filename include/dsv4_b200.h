@@ -179,6 +179,22 @@ int mxfp4_moe_forward_ep(const uint16_t* x, const uint8_t* bank_W1_packed, const
 int mxfp4_moe_ep_sum(const uint16_t* recv, const int* ids, int k, int experts_per_rank, int world, int n_tokens,
                      int out_dim, uint16_t* out, void* stream);
 
+/* Expert parallel with both sides over peer memory (no collective library on the path).  Every rank has published
+ * its tokens in buffers mapped on all ranks: x bf16 [tokens_per_rank, K_in], ids int32 [tokens_per_rank, k] (global
+ * expert ids), weights FP32 [tokens_per_rank, k]; x_ptrs / ids_ptrs / w_ptrs / recv_ptrs are HOST arrays of `world`
+ * device pointers (entry r = rank r's buffer).  After a barrier over the ranks this call runs the rank's
+ * n_experts_local experts over all world * tokens_per_rank tokens, reading each token from the rank that published
+ * it and storing the partial rows into the home ranks' receive buffers as mxfp4_moe_forward_ep does; after a second
+ * barrier every rank calls mxfp4_moe_ep_sum.  Block-scaled tensor-core path.  workspace:
+ * mxfp4_moe_forward_ep2_workspace_bytes.  Return codes as mxfp4_moe_forward_ep. */
+size_t mxfp4_moe_forward_ep2_workspace_bytes(int world, int tokens_per_rank, int k, int K_in, int hidden, int out_dim,
+                                             int n_experts_local);
+int mxfp4_moe_forward_ep2(void* const* x_ptrs, void* const* ids_ptrs, void* const* w_ptrs,
+                          const uint8_t* bank_W1_packed, const uint8_t* bank_W3_packed, const uint8_t* bank_W2_packed,
+                          const uint8_t* bank_W1_scale, const uint8_t* bank_W3_scale, const uint8_t* bank_W2_scale,
+                          int tokens_per_rank, int n_experts_local, int K_in, int hidden, int out_dim, int k,
+                          void* const* recv_ptrs, int world, int my_rank, void* workspace, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -45,6 +45,11 @@ for rep in range(3):                                      # alternating receive 
     assert err <= 1e-2, ("peer", rep, err)
     again = ep.ep_moe_forward_peer(ctx, x, ids, w, E, local_bank)
     assert torch.equal(again.view(torch.int16), out.to(torch.bfloat16).view(torch.int16))
+ctx2 = ep.PeerCombine(T, K, dev, in_dim=K, k=k)
+for rep in range(3):                                      # inputs read from the peers' published buffers too
+    out = ep.ep_moe_forward_peer_inputs(ctx2, x, ids, w, E, local_bank).float()
+    err = float((out - ref).abs().max() / ref.abs().max())
+    assert err <= 1e-2, ("peer inputs", rep, err)
 torch.cuda.synchronize()
 assert rt.moe_device_status() == 0
 dist.barrier()
