@@ -423,6 +423,38 @@ def dense_configs(rt, qz, torch, dev):
         [(lambda sh=sh: rt.fp8_shared_swiglu(sh, x, out=y2, workspace=ws2)) for sh in banks], shared_bytes)
     out["shared_expert_fp8_swiglu_three_gemv_calls"] = timed([(lambda sh=sh: three_calls(sh)) for sh in banks], shared_bytes)
     del banks
+    # attention projections through fp8_e4m3_gemv_batched and the loops of single calls they replace:
+    # wo_a = 8 groups x (4096 -> 1024) for one token; wq_b (1024 -> 32768) for 4 tokens
+    groups, n_g, copies3 = 8, 1024, 10
+    mats = [qz.quantize_fp8_block128(torch.randn(groups * n_g, HIDDEN, generator=g, device=dev) * 0.02, "e8m0")
+            for _ in range(copies3)]
+    xg = torch.randn(groups * HIDDEN, generator=g, device=dev).to(torch.bfloat16)
+    yg = torch.empty(groups * n_g, dtype=torch.bfloat16, device=dev)
+
+    def wo_a_loop(m):
+        for i in range(groups):
+            rt.fp8_e4m3_gemv(m[0][i * n_g:(i + 1) * n_g], m[1][i * n_g // 128:(i + 1) * n_g // 128],
+                             xg[i * HIDDEN:(i + 1) * HIDDEN], out=yg[i * n_g:(i + 1) * n_g])
+
+    nbytes = groups * n_g * HIDDEN + groups * (n_g // 128) * (HIDDEN // 128) + groups * HIDDEN * 2 + groups * n_g * 2
+    out["attn_wo_a_8_groups_4096_to_1024_one_launch"] = timed(
+        [(lambda m=m: rt.fp8_e4m3_gemv_batched(m[0], m[1], xg, n_groups=groups, out=yg)) for m in mats], nbytes)
+    out["attn_wo_a_8_groups_4096_to_1024_eight_calls"] = timed([(lambda m=m: wo_a_loop(m)) for m in mats], nbytes)
+    del mats
+    toks, kq, nq = 4, 1024, 32768
+    mats = [qz.quantize_fp8_block128(torch.randn(nq, kq, generator=g, device=dev) * 0.02, "e8m0") for _ in range(copies3)]
+    xq = torch.randn(toks, kq, generator=g, device=dev).to(torch.bfloat16)
+    yq = torch.empty(toks, nq, dtype=torch.bfloat16, device=dev)
+
+    def wq_b_loop(m):
+        for t in range(toks):
+            rt.fp8_e4m3_gemv(m[0], m[1], xq[t], out=yq[t])
+
+    nbytes = nq * kq + (nq // 128) * (kq // 128) + toks * kq * 2 + toks * nq * 2
+    out["attn_wq_b_1024_to_32768_4_tokens_one_launch"] = timed(
+        [(lambda m=m: rt.fp8_e4m3_gemv_batched(m[0], m[1], xq, out=yq)) for m in mats], nbytes)
+    out["attn_wq_b_1024_to_32768_4_tokens_four_calls"] = timed([(lambda m=m: wq_b_loop(m)) for m in mats], nbytes)
+    del mats
     torch.cuda.empty_cache()
     return out
 

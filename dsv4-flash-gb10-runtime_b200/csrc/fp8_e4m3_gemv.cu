@@ -110,3 +110,57 @@ DSV4_API int fp8_e4m3_shared_swiglu_m1(const __nv_bfloat16* x, const uint8_t* W1
     }
     return 0;
 }
+
+// Additive: the FP8 GEMV for several tokens and several independent groups in one launch - what the reference
+// issues as a loop of fp8_e4m3_gemv_m1 calls: one per token in the Python engine's _fp8_linear
+// (runtime/dsv4_engine_mxfp4.py:310-320) and one per group for the grouped output projection wo_a
+// (kernel/cpp-engine-mxfp4/dsv4_engine_mxfp4_wire.cu:484-498).
+//   y[t, g*N + n] = bf16( sum_k e4m3(W[g*N + n, k]) * 2^(S[(g*N + n)/128, k/128] - 127) * x[t, g*K + k] )
+// W_fp8 [n_groups*N, K], W_scale [n_groups*N/128, K/128] E8M0, row strides in bytes; x [n_tokens, >= n_groups*K],
+// y [n_tokens, >= n_groups*N] bf16 with token strides in ELEMENTS.  n_groups = 1 is the batched GEMV; n_tokens = 1,
+// n_groups = 8, K = 4096, N = 1024 is wo_a.  Every weight byte is read once per 4 tokens.  A row of y is bit-identical
+// to what fp8_e4m3_gemv_m1 returns for that token and group.
+// Returns 0, -1 (K % 128), -2 (N % 128), -3 (K > 16384), -4 (launch failure), -8 (null pointer, n_groups < 1,
+// negative n_tokens, a token stride shorter than a row, or x / W / a stride that is not 16-byte aligned: this entry
+// has no byte-wise path).  n_tokens == 0 or N == 0 is a no-op.
+DSV4_API int fp8_e4m3_gemv_batched(const __nv_bfloat16* x, const uint8_t* W_fp8, const uint8_t* W_scale, int K, int N,
+                                   int64_t weight_row_stride_bytes, int64_t scale_row_stride_bytes, int n_groups,
+                                   int n_tokens, int64_t x_token_stride, int64_t y_token_stride, __nv_bfloat16* y,
+                                   cudaStream_t stream) {
+    if (K <= 0 || K % 128 != 0) {
+        std::fprintf(stderr, "fp8_e4m3_gemv_batched: K=%d not a positive multiple of 128\n", K);
+        return -1;
+    }
+    if (N < 0 || N % 128 != 0) {
+        std::fprintf(stderr, "fp8_e4m3_gemv_batched: N=%d not a multiple of 128\n", N);
+        return -2;
+    }
+    if (K > 16384) {
+        std::fprintf(stderr, "fp8_e4m3_gemv_batched: K=%d > 16384\n", K);
+        return -3;
+    }
+    if (n_groups < 1 || n_tokens < 0 || x_token_stride < (int64_t)n_groups * K || y_token_stride < (int64_t)n_groups * N) {
+        std::fprintf(stderr, "fp8_e4m3_gemv_batched: bad group / token layout\n");
+        return -8;
+    }
+    if (N == 0 || n_tokens == 0) return 0;
+    if (!x || !W_fp8 || !W_scale || !y) {
+        std::fprintf(stderr, "fp8_e4m3_gemv_batched: null pointer\n");
+        return -8;
+    }
+    DenseMultiArgs m;
+    m.a.x = x; m.a.w = W_fp8; m.a.s = W_scale; m.a.K = K; m.a.N = N;
+    m.a.w_stride = weight_row_stride_bytes; m.a.s_stride = scale_row_stride_bytes; m.a.y = y;
+    m.n_groups = n_groups; m.n_tok = n_tokens; m.x_tok = x_token_stride; m.y_tok = y_token_stride;
+    const cudaError_t err = dense_multi_launch<Fp8Scale>(m, stream);
+    if (err == cudaErrorInvalidValue) {
+        (void)cudaGetLastError();
+        std::fprintf(stderr, "fp8_e4m3_gemv_batched: x, W and the strides must be 16-byte aligned\n");
+        return -8;
+    }
+    if (err != cudaSuccess) {
+        std::fprintf(stderr, "fp8_e4m3_gemv_batched launch failed: %s\n", cudaGetErrorString(err));
+        return -4;
+    }
+    return 0;
+}

@@ -39,6 +39,8 @@ SIGNATURES = {
     "fp8": {
         "fp8_e4m3_gemv_m1": (c_int, [_P, _P, _P, c_int, c_int, c_int64, c_int64, _P, _P]),
         "fp8_e4m3_gemv_m1_f32scale": (c_int, [_P, _P, _P, c_int, c_int, c_int64, c_int64, _P, _P]),
+        "fp8_e4m3_gemv_batched": (c_int, [_P, _P, _P, c_int, c_int, c_int64, c_int64, c_int, c_int, c_int64, c_int64,
+                                          _P, _P]),
         "fp8_e4m3_shared_swiglu_workspace_bytes": (c_size_t, [c_int]),
         "fp8_e4m3_shared_swiglu_m1": (c_int, [_P] * 7 + [c_int] * 3 + [c_float] * 2 + [_P] * 3),
     },

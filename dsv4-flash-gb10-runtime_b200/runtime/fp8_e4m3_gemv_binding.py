@@ -67,6 +67,58 @@ def fp8_e4m3_gemv_f32scale(W_fp8: torch.Tensor, W_scale: torch.Tensor, x: torch.
     return _run("fp8_e4m3_gemv_m1_f32scale", torch.float32, W_fp8, W_scale, x, out, stream)
 
 
+def fp8_e4m3_gemv_batched(W_fp8: torch.Tensor, W_scale: torch.Tensor, x: torch.Tensor, n_groups: int = 1,
+                          out: Optional[torch.Tensor] = None,
+                          stream: Optional[torch.cuda.Stream] = None) -> torch.Tensor:
+    """Several tokens and / or several independent groups in one launch - what the reference does as a loop of
+    fp8_e4m3_gemv calls, one per token (`_fp8_linear`, runtime/dsv4_engine_mxfp4.py:310-320) and one per group of the
+    grouped output projection (kernel/cpp-engine-mxfp4/dsv4_engine_mxfp4_wire.cu:484-498):
+
+        y[t, g*N + n] = sum_k W[g*N + n, k] * x[t, g*K + k]
+
+    W_fp8 uint8 [n_groups*N, K], W_scale uint8 [n_groups*N/128, K/128], x bfloat16 [n_groups*K] or [S, n_groups*K];
+    returns bfloat16 [n_groups*N] or [S, n_groups*N].  Each row equals the single-token operator's result bit for bit."""
+    _require(W_fp8.is_cuda and W_scale.is_cuda and x.is_cuda, "all tensors must be on CUDA device")
+    _require(W_fp8.dtype == torch.uint8, f"W_fp8 must be uint8 (raw E4M3), got {W_fp8.dtype}")
+    _require(W_scale.dtype == torch.uint8, f"W_scale must be uint8 (E8M0), got {W_scale.dtype}")
+    _require(x.dtype == torch.bfloat16, f"x must be bfloat16, got {x.dtype}")
+    _require(x.dim() in (1, 2), f"x must be [G*K] or [S, G*K], got shape {tuple(x.shape)}")
+    _require(W_fp8.dim() == 2 and W_scale.dim() == 2, "W_fp8 and W_scale must be 2-D")
+    _require(n_groups >= 1, f"n_groups={n_groups} must be >= 1")
+    single = x.dim() == 1
+    xs = x.unsqueeze(0) if single else x
+    S, K = xs.shape[0], W_fp8.shape[1]
+    _require(xs.shape[1] == n_groups * K, f"x row length {xs.shape[1]} != n_groups*K = {n_groups * K}")
+    _require(W_fp8.shape[0] % n_groups == 0, f"W_fp8 rows {W_fp8.shape[0]} not divisible by n_groups={n_groups}")
+    N = W_fp8.shape[0] // n_groups
+    _require(K % FP8_BLOCK_TILE == 0, f"K={K} must be multiple of {FP8_BLOCK_TILE}")
+    _require(N % FP8_BLOCK_TILE == 0, f"N={N} must be multiple of {FP8_BLOCK_TILE}")
+    want = (n_groups * N // FP8_BLOCK_TILE, K // FP8_BLOCK_TILE)
+    _require(tuple(W_scale.shape) == want, f"W_scale shape {tuple(W_scale.shape)} != {want}")
+    if W_fp8.stride(1) != 1:
+        W_fp8 = W_fp8.contiguous()
+    if W_scale.stride(1) != 1:
+        W_scale = W_scale.contiguous()
+    if xs.stride(1) != 1:
+        xs = xs.contiguous()
+    if out is None:
+        out2 = torch.empty(S, n_groups * N, dtype=torch.bfloat16, device=x.device)
+    else:
+        shape = (n_groups * N,) if single else (S, n_groups * N)
+        _require(tuple(out.shape) == shape and out.dtype == torch.bfloat16 and out.is_cuda and out.stride(-1) == 1,
+                 f"out must be a cuda bfloat16 {list(shape)} with unit inner stride")
+        out2 = out.unsqueeze(0) if single else out
+    lib = _capi.load("fp8")
+    rc = lib.fp8_e4m3_gemv_batched(_capi.ptr(xs), _capi.ptr(W_fp8), _capi.ptr(W_scale), c_int(K), c_int(N),
+                                   c_int64(W_fp8.stride(0)), c_int64(W_scale.stride(0)), c_int(n_groups), c_int(S),
+                                   c_int64(xs.stride(0) if S > 1 else n_groups * K),
+                                   c_int64(out2.stride(0) if S > 1 else n_groups * N), _capi.ptr(out2),
+                                   _capi.stream_ptr(x.device, stream))
+    if rc != 0:
+        raise RuntimeError(f"fp8_e4m3_gemv_batched returned {rc}")
+    return out2[0] if single else out2
+
+
 def fp8_shared_swiglu(shared: dict, x: torch.Tensor, limit_gate: float = 10.0, limit_up: float = 0.0,
                       out: Optional[torch.Tensor] = None, workspace: Optional[torch.Tensor] = None,
                       stream: Optional[torch.cuda.Stream] = None) -> torch.Tensor:
@@ -103,4 +155,4 @@ def fp8_shared_swiglu(shared: dict, x: torch.Tensor, limit_gate: float = 10.0, l
     return out
 
 
-__all__ = ["fp8_e4m3_gemv", "fp8_e4m3_gemv_f32scale", "fp8_shared_swiglu", "FP8_BLOCK_TILE"]
+__all__ = ["fp8_e4m3_gemv", "fp8_e4m3_gemv_f32scale", "fp8_e4m3_gemv_batched", "fp8_shared_swiglu", "FP8_BLOCK_TILE"]

@@ -123,6 +123,19 @@ int fp8_e4m3_gemv_m1_f32scale(const uint16_t* x, const uint8_t* W_fp8, const flo
                               int64_t weight_row_stride_bytes, int64_t scale_row_stride_bytes, uint16_t* y,
                               void* stream);
 
+/* Added: several tokens and several independent groups in one launch - what the reference issues as a loop of
+ * fp8_e4m3_gemv_m1 calls, one per token (runtime/dsv4_engine_mxfp4.py:310-320) and one per group of the grouped
+ * output projection wo_a (kernel/cpp-engine-mxfp4/dsv4_engine_mxfp4_wire.cu:484-498):
+ *   y[t, g*N + n] = bf16(sum_k e4m3(W[g*N + n, k]) 2^(S[(g*N + n)/128, k/128]-127) x[t, g*K + k]).
+ * W_fp8 [n_groups*N, K], W_scale [n_groups*N/128, K/128] E8M0, row strides in bytes; x [n_tokens, >= n_groups*K] and
+ * y [n_tokens, >= n_groups*N] bf16 with token strides in elements.  Every weight byte is read once per 4 tokens; a row
+ * of y is bit-identical to fp8_e4m3_gemv_m1 for that token and group.  Returns -1 K % 128, -2 N % 128, -3 K > 16384,
+ * -4 launch failure, -8 null pointer, n_groups < 1, n_tokens < 0, a token stride shorter than a row, or x / W /
+ * a stride that is not 16-byte aligned (no byte-wise path here). */
+int fp8_e4m3_gemv_batched(const uint16_t* x, const uint8_t* W_fp8, const uint8_t* W_scale, int K, int N,
+                          int64_t weight_row_stride_bytes, int64_t scale_row_stride_bytes, int n_groups, int n_tokens,
+                          int64_t x_token_stride, int64_t y_token_stride, uint16_t* y, void* stream);
+
 /* Added: the shared expert's gated FFN for one token, all FP8 - what the reference composes from three
  * fp8_e4m3_gemv_m1 calls and an activation kernel (kernel/cpp-engine-mxfp4/dsv4_engine_mxfp4_wire.cu:523-556; Python
  * twin runtime/dsv4_engine_mxfp4.py:399-410): g = bf16(W1 x), u = bf16(W3 x),
