@@ -406,6 +406,10 @@ inline cudaError_t dense_launch(const DenseArgs& a, cudaStream_t stream) {
     return cudaLaunchKernelEx(&cfg, dense_gemv_kernel<Fmt, Sc>, a);
 }
 
+template <class Sc>
+inline cudaError_t dense_mma_launch(const DenseMultiArgs& m, cudaStream_t stream);      // dense_mma_gemv.cuh
+constexpr int kMmaPanel = 2048;        // K elements of activations the MMA kernel stages at a time
+
 // Several tokens / groups: needs 16-byte aligned x, weights, row strides and token strides (cudaErrorInvalidValue
 // otherwise).  grid.y = groups; at most kDenseCap rows per CTA.  One token goes through dense_gemv_kernel.
 template <class Sc>
@@ -428,8 +432,9 @@ inline cudaError_t dense_multi_launch(const DenseMultiArgs& m, cudaStream_t stre
     cfg.attrs = attr;
     cfg.numAttrs = dense_pdl_enabled() ? 1 : 0;
     if (m.n_tok == 1) return cudaLaunchKernelEx(&cfg, dense_gemv_kernel<Fp8Format, Sc, true>, a);
-    if (m.n_tok == 2) return cudaLaunchKernelEx(&cfg, dense_multi_gemv_kernel<Sc, 2, 4>, m);
-    return cudaLaunchKernelEx(&cfg, dense_multi_gemv_kernel<Sc, 4, 4>, m);
+    // two tokens over a long K: the per-lane products still win (the MMA kernel restages its activations per 2048 K)
+    if (m.n_tok == 2 && a.K > kMmaPanel) return cudaLaunchKernelEx(&cfg, dense_multi_gemv_kernel<Sc, 2, 4>, m);
+    return dense_mma_launch<Sc>(m, stream);
 }
 
 // The gate / up pair: ag and au describe the two matrices (same K, N, x); the activation goes to ag.y.

@@ -2,6 +2,7 @@
 // Drop-in for the reference's kernel/fp8-dense/fp8_e4m3_gemv.cu:132-174 (same symbol, argument order and
 // return codes).  The kernel itself is in dense_gemv.cuh.
 #include "dense_gemv.cuh"
+#include "dense_mma_gemv.cuh"
 
 using namespace dsv4;
 
@@ -118,8 +119,9 @@ DSV4_API int fp8_e4m3_shared_swiglu_m1(const __nv_bfloat16* x, const uint8_t* W1
 //   y[t, g*N + n] = bf16( sum_k e4m3(W[g*N + n, k]) * 2^(S[(g*N + n)/128, k/128] - 127) * x[t, g*K + k] )
 // W_fp8 [n_groups*N, K], W_scale [n_groups*N/128, K/128] E8M0, row strides in bytes; x [n_tokens, >= n_groups*K],
 // y [n_tokens, >= n_groups*N] bf16 with token strides in ELEMENTS.  n_groups = 1 is the batched GEMV; n_tokens = 1,
-// n_groups = 8, K = 4096, N = 1024 is wo_a.  Every weight byte is read once per 4 tokens.  A row of y is bit-identical
-// to what fp8_e4m3_gemv_m1 returns for that token and group.
+// n_groups = 8, K = 4096, N = 1024 is wo_a.  Every weight byte is read once per 8 tokens.  With one token a row of y is
+// bit-identical to what fp8_e4m3_gemv_m1 returns for that group; with several tokens the sums are formed by FP32
+// tensor-core MMAs (dense_mma_gemv.cuh) and agree with it to the last bf16 step.
 // Returns 0, -1 (K % 128), -2 (N % 128), -3 (K > 16384), -4 (launch failure), -8 (null pointer, n_groups < 1,
 // negative n_tokens, a token stride shorter than a row, or x / W / a stride that is not 16-byte aligned: this entry
 // has no byte-wise path).  n_tokens == 0 or N == 0 is a no-op.

@@ -77,7 +77,8 @@ def fp8_e4m3_gemv_batched(W_fp8: torch.Tensor, W_scale: torch.Tensor, x: torch.T
         y[t, g*N + n] = sum_k W[g*N + n, k] * x[t, g*K + k]
 
     W_fp8 uint8 [n_groups*N, K], W_scale uint8 [n_groups*N/128, K/128], x bfloat16 [n_groups*K] or [S, n_groups*K];
-    returns bfloat16 [n_groups*N] or [S, n_groups*N].  Each row equals the single-token operator's result bit for bit."""
+    returns bfloat16 [n_groups*N] or [S, n_groups*N].  With one token the result equals the single-token operator's bit
+    for bit; with several tokens it agrees with it to the last bfloat16 step (FP32 tensor-core sums)."""
     _require(W_fp8.is_cuda and W_scale.is_cuda and x.is_cuda, "all tensors must be on CUDA device")
     _require(W_fp8.dtype == torch.uint8, f"W_fp8 must be uint8 (raw E4M3), got {W_fp8.dtype}")
     _require(W_scale.dtype == torch.uint8, f"W_scale must be uint8 (E8M0), got {W_scale.dtype}")

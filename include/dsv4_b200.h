@@ -128,8 +128,9 @@ int fp8_e4m3_gemv_m1_f32scale(const uint16_t* x, const uint8_t* W_fp8, const flo
  * output projection wo_a (kernel/cpp-engine-mxfp4/dsv4_engine_mxfp4_wire.cu:484-498):
  *   y[t, g*N + n] = bf16(sum_k e4m3(W[g*N + n, k]) 2^(S[(g*N + n)/128, k/128]-127) x[t, g*K + k]).
  * W_fp8 [n_groups*N, K], W_scale [n_groups*N/128, K/128] E8M0, row strides in bytes; x [n_tokens, >= n_groups*K] and
- * y [n_tokens, >= n_groups*N] bf16 with token strides in elements.  Every weight byte is read once per 4 tokens; a row
- * of y is bit-identical to fp8_e4m3_gemv_m1 for that token and group.  Returns -1 K % 128, -2 N % 128, -3 K > 16384,
+ * y [n_tokens, >= n_groups*N] bf16 with token strides in elements.  Every weight byte is read once per 8 tokens.  With
+ * one token a row of y is bit-identical to fp8_e4m3_gemv_m1 for that group; with several tokens (FP32 tensor-core
+ * sums) it agrees with it to the last bf16 step.  Returns -1 K % 128, -2 N % 128, -3 K > 16384,
  * -4 launch failure, -8 null pointer, n_groups < 1, n_tokens < 0, a token stride shorter than a row, or x / W /
  * a stride that is not 16-byte aligned (no byte-wise path here). */
 int fp8_e4m3_gemv_batched(const uint16_t* x, const uint8_t* W_fp8, const uint8_t* W_scale, int K, int N,

@@ -1,7 +1,8 @@
 """GPU parity of fp8_e4m3_gemv_batched (several tokens / several independent groups in one launch) against the CPU
-oracle and, bit for bit, against the loop of single-token fp8_e4m3_gemv calls it replaces: the per-token loop of the
-reference's `_fp8_linear` (runtime/dsv4_engine_mxfp4.py:310-320) and the per-group loop of the grouped output
-projection (kernel/cpp-engine-mxfp4/dsv4_engine_mxfp4_wire.cu:484-498).  Shapes are the attention projections'
+oracle and against the loop of single-token fp8_e4m3_gemv calls it replaces (bit for bit with one token, where the
+same kernel runs per group; to rounding with several tokens, where the sums are formed by FP32 tensor-core MMAs):
+the per-token loop of the reference's `_fp8_linear` (runtime/dsv4_engine_mxfp4.py:310-320) and the per-group loop of
+the grouped output projection (kernel/cpp-engine-mxfp4/dsv4_engine_mxfp4_wire.cu:484-498).  Shapes are the attention projections'
 (K -> N): wq_a 4096 -> 1024, wq_b 1024 -> 32768, wkv 4096 -> 512, wo_a 8 x (4096 -> 1024), wo_b 8192 -> 4096."""
 from ctypes import c_int, c_int64
 
@@ -30,8 +31,12 @@ def bits(t):
     ("wkv", 4096, 512, 1, 7),
     ("wq_b", 1024, 32768, 1, 4),
     ("wo_a", 4096, 1024, 8, 1),
+    ("wo_a", 4096, 1024, 8, 2),
     ("wo_a", 4096, 1024, 8, 5),
     ("wo_b", 8192, 4096, 1, 9),
+    ("wo_b", 8192, 4096, 1, 17),
+    ("long_k", 16384, 256, 1, 3),
+    ("odd_k", 2048 + 384, 128, 2, 8),
     ("small", 128, 128, 3, 6),
     ("ragged", 384, 640, 2, 2),
 ])
@@ -46,9 +51,15 @@ def test_batched_matches_oracle_and_single_calls(rt, qz, name, K, N, G, S):
         for g in range(G):
             one = rt.fp8_e4m3_gemv(wd[g * N:(g + 1) * N], sd[g * N // 128:(g + 1) * N // 128],
                                    xd[t, g * K:(g + 1) * K].contiguous())
-            assert torch.equal(bits(one), bits(y[t, g * N:(g + 1) * N])), f"{name}: token {t} group {g} differs"
-    # the oracle on a bounded number of (token, group) pairs: the bit-equality above carries the rest
-    for t, g in {(0, 0), (S - 1, G - 1)}:
+            got = y[t, g * N:(g + 1) * N]
+            if S == 1:
+                assert torch.equal(bits(one), bits(got)), f"{name}: group {g} differs from the single call"
+            else:
+                # both are bf16 roundings of sums that differ in the last FP32 bits: at most one bf16 step apart
+                d = (one.float() - got.float()).abs().max() / one.float().abs().max()
+                assert float(d) <= 2.0 ** -7, f"{name}: token {t} group {g}: {float(d):.3e} from the single call"
+    # the oracle on a bounded number of (token, group) pairs: the comparison above carries the rest
+    for t, g in {(0, 0), (S - 1, G - 1), (S // 2, G // 2)}:
         ref = oracle.fp8_gemv_ref(w[g * N:(g + 1) * N], s[g * N // 128:(g + 1) * N // 128], x[t, g * K:(g + 1) * K])
         got = y[t, g * N:(g + 1) * N].float().cpu().numpy()
         err, cos = oracle.max_abs_rel(got, ref), oracle.cosine(got, ref)
