@@ -47,18 +47,16 @@ struct Fp8ScaleF32 {   // FP32 [N/128, K/128], row stride in bytes
     __device__ static __forceinline__ float value(uint32_t raw) { return __uint_as_float(raw); }
 };
 
-template <int R>
-struct DenseBatchT {
-    uint4 w[R];
-    uint32_t s[R];
+struct DenseBatch {
+    uint4 w[kDenseRows];
+    uint32_t s[kDenseRows];
 };
-using DenseBatch = DenseBatchT<kDenseRows>;
 
-template <class Sc, int R = kDenseRows>
+template <class Sc>
 __device__ __forceinline__ void dense_issue(const DenseArgs& a, int row, int step, int row_end, int blk,
-                                            bool lane_ok, DenseBatchT<R>& b) {
+                                            bool lane_ok, DenseBatch& b) {
 #pragma unroll
-    for (int i = 0; i < R; ++i) {
+    for (int i = 0; i < kDenseRows; ++i) {
         const int n = row + i * step;
         b.w[i] = make_uint4(0, 0, 0, 0);
         b.s[i] = 0;
@@ -209,126 +207,15 @@ __global__ void __launch_bounds__(kDenseThreads, 2) dense_dual_swiglu_kernel(con
 
 // Several tokens and several independent groups in one launch (FP8 only: the attention projections):
 //   y[t, g*N + n] = bf16( sum_k W[g*N + n, k] * x[t, g*K + k] ),   W [G*N, K], scales [G*N/128, K/128].
-// G = 1 is a plain batched GEMV that reads every weight byte once for up to T tokens; G > 1 is the block-diagonal
-// shape of the grouped output projection (one launch instead of G).  blockIdx.y is the group; a
-// CTA owns a row range of one group and streams it once per chunk of T tokens: a weight block is decoded once and
-// multiplied with the T activation blocks the lane holds.  The per-token arithmetic (decode, fp16x2 products,
-// FP32 slice sums, their order) is that of dense_gemv_kernel, so a row of y equals the M = 1 kernel's bit for bit.
+// G = 1 is a plain batched GEMV; G > 1 is the block-diagonal shape of the grouped output projection (one launch
+// instead of G).  One token runs the grouped form of dense_gemv_kernel (bit-identical to the M = 1 entry); several
+// tokens run dense_mma_gemv_kernel (dense_mma_gemv.cuh), which reads every weight byte once per 8 tokens.
 struct DenseMultiArgs {
     DenseArgs a;                   // group 0, token 0; a.N = rows per group
     int n_groups;
     int n_tok;
     long long x_tok, y_tok;        // elements between consecutive tokens of x / y
 };
-
-// T tokens per pass, R rows per warp batch: (2, 4) and (4, 4) fit 128 registers, two CTAs resident per SM.
-template <class Sc, int T, int R>
-__device__ __forceinline__ void dense_multi_consume(const DenseBatchT<R>& b, const ActBlock<Fp8Format> (&xb)[T],
-                                                    int lane, int local0, int step, int n_local, int ks,
-                                                    float (*part)[kDenseCap][kDenseMaxSlices]) {
-    float v[T * R];        // [token][row], reduced together: T * R values cost one butterfly
-#pragma unroll
-    for (int i = 0; i < R; ++i) {
-        const bool live = local0 + i * step < n_local;
-        const float sc = Sc::value(b.s[i]);
-        const uint32_t word[4] = {b.w[i].x, b.w[i].y, b.w[i].z, b.w[i].w};
-        __half2 wh[8];
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-            __half2 h[2];
-            e4m3x4_to_h2x2(word[j], h);
-            wh[2 * j] = h[0];
-            wh[2 * j + 1] = h[1];
-        }
-#pragma unroll
-        for (int t = 0; t < T; ++t) {
-            __half2 acc[4];
-#pragma unroll
-            for (int j = 0; j < 4; ++j) {
-                acc[j] = __hmul2(wh[2 * j], xb[t].h[2 * j]);
-                acc[j] = __hfma2(wh[2 * j + 1], xb[t].h[2 * j + 1], acc[j]);
-            }
-            const float2 f01 = __half22float2(__hadd2(acc[0], acc[1]));
-            const float2 f23 = __half22float2(__hadd2(acc[2], acc[3]));
-            const float d = (f01.x + f01.y) + (f23.x + f23.y);
-            v[t * R + i] = live ? d * (sc * xb[t].scale) : 0.f;
-        }
-    }
-    // the butterfly visits the lane offsets 16, 8, 4, 2, 1 whatever the number of values, so a sum has the same
-    // bits as in dense_consume
-    multi_reduce<T * R>(v, lane);
-    if (multi_reduce_owner<T * R>(lane)) {
-        const int idx = multi_reduce_index<T * R>(lane);
-        const int local = local0 + (idx % R) * step;
-        if (local < n_local) part[idx / R][local][ks] = v[0];
-    }
-}
-
-template <class Sc, int T, int R>
-__global__ void __launch_bounds__(kDenseThreads, 2) dense_multi_gemv_kernel(const DenseMultiArgs m) {
-    using Fmt = Fp8Format;
-    __shared__ float part[T][kDenseCap][kDenseMaxSlices];
-    pdl_launch_dependents();
-
-    const int lane = threadIdx.x & 31;
-    const int warp = threadIdx.x >> 5;
-    const int n_warps = blockDim.x >> 5;
-    const int grp = blockIdx.y;
-
-    DenseArgs a = m.a;
-    a.x += (long long)grp * a.K;
-    a.w += (long long)grp * a.N * a.w_stride;
-    a.s += (long long)grp * (a.N >> 7) * a.s_stride;
-    a.y += (long long)grp * a.N;
-
-    const int n_blk = a.K / Fmt::kElems;
-    const int n_slices = (n_blk + 31) >> 5;
-    const int n_groups = max(1, n_warps / n_slices);
-    const int n_tasks = n_slices * n_groups;
-    const int r_begin = (int)((long long)a.N * blockIdx.x / gridDim.x);
-    const int r_end = (int)((long long)a.N * (blockIdx.x + 1) / gridDim.x);
-    const int n_local = r_end - r_begin;
-    const int span = R * n_groups;
-
-    bool waited = false;
-    for (int tok0 = 0; tok0 < m.n_tok; tok0 += T) {
-        const int nt = min(T, m.n_tok - tok0);
-        for (int task = warp; task < n_tasks; task += n_warps) {
-            const int ks = task % n_slices;
-            const int rg = task / n_slices;
-            const int blk = ks * 32 + lane;
-            const bool lane_ok = blk < n_blk;
-
-            DenseBatchT<R> b0, b1;
-            dense_issue<Sc, R>(a, r_begin + rg, n_groups, r_end, blk, lane_ok, b0);
-            if (!waited) { pdl_wait(); waited = true; }
-
-            ActBlock<Fmt> xb[T];
-#pragma unroll
-            for (int t = 0; t < T; ++t)
-                act_block_load_bf16<Fmt>(a.x + (long long)(tok0 + min(t, nt - 1)) * m.x_tok + (size_t)blk * Fmt::kElems,
-                                         lane_ok, xb[t]);
-
-            for (int local0 = rg; local0 < n_local; local0 += 2 * span) {
-                dense_issue<Sc, R>(a, r_begin + local0 + span, n_groups, r_end, blk, lane_ok, b1);
-                dense_multi_consume<Sc, T, R>(b0, xb, lane, local0, n_groups, n_local, ks, part);
-                dense_issue<Sc, R>(a, r_begin + local0 + 2 * span, n_groups, r_end, blk, lane_ok, b0);
-                dense_multi_consume<Sc, T, R>(b1, xb, lane, local0 + span, n_groups, n_local, ks, part);
-            }
-        }
-        if (!waited) { pdl_wait(); waited = true; }
-        __syncthreads();
-        for (int i = threadIdx.x; i < n_local * nt; i += blockDim.x) {
-            const int t = i / n_local;
-            const int row = i - t * n_local;
-            float acc = 0.f;
-            for (int s = 0; s < n_slices; ++s) acc += part[t][row][s];
-            a.y[(long long)(tok0 + t) * m.y_tok + r_begin + row] = __float2bfloat16(acc);
-        }
-        __syncthreads();
-    }
-    if (!waited) pdl_wait();
-}
 
 // Any alignment, any stride: one warp per row, byte loads, FP32 FMA.  Only taken when a base pointer
 // or a row stride is not a multiple of 16 bytes.
@@ -408,10 +295,9 @@ inline cudaError_t dense_launch(const DenseArgs& a, cudaStream_t stream) {
 
 template <class Sc>
 inline cudaError_t dense_mma_launch(const DenseMultiArgs& m, cudaStream_t stream);      // dense_mma_gemv.cuh
-constexpr int kMmaPanel = 2048;        // K elements of activations the MMA kernel stages at a time
 
 // Several tokens / groups: needs 16-byte aligned x, weights, row strides and token strides (cudaErrorInvalidValue
-// otherwise).  grid.y = groups; at most kDenseCap rows per CTA.  One token goes through dense_gemv_kernel.
+// otherwise).  One token: grid.y = groups, at most kDenseCap rows per CTA.
 template <class Sc>
 inline cudaError_t dense_multi_launch(const DenseMultiArgs& m, cudaStream_t stream) {
     const DenseArgs& a = m.a;
@@ -432,8 +318,6 @@ inline cudaError_t dense_multi_launch(const DenseMultiArgs& m, cudaStream_t stre
     cfg.attrs = attr;
     cfg.numAttrs = dense_pdl_enabled() ? 1 : 0;
     if (m.n_tok == 1) return cudaLaunchKernelEx(&cfg, dense_gemv_kernel<Fp8Format, Sc, true>, a);
-    // two tokens over a long K: the per-lane products still win (the MMA kernel restages its activations per 2048 K)
-    if (m.n_tok == 2 && a.K > kMmaPanel) return cudaLaunchKernelEx(&cfg, dense_multi_gemv_kernel<Sc, 2, 4>, m);
     return dense_mma_launch<Sc>(m, stream);
 }
 
