@@ -91,6 +91,29 @@ def test_token_strides_wider_than_a_row(rt, qz):
     assert bool((yw[:, N:] == 7.0).all()), "columns beyond N must stay untouched"
 
 
+def test_activation_magnitudes_across_the_bf16_range(rt, qz):
+    """Tokens of very different magnitude in one pass: every (token, 2048-element half) carries its own power-of-two
+    scale into the fp16 operands, so each row must match the single-token operator as closely as at unit scale."""
+    K, N = 4096, 512
+    w, s = make(qz, N, K, seed=11)
+    wd, sd = w.to(DEV), s.to(DEV)
+    scales = [1e-30, 1e-6, 1.0, 3e4, 1e20, 1e30, 0.0]
+    x = torch.randn(len(scales), K, generator=torch.Generator().manual_seed(12))
+    # one outlier per row: the rest of the row sits 2^10 below the largest magnitude
+    x[:, 7] *= 1024.0
+    x = (x * torch.tensor(scales).unsqueeze(1)).to(torch.bfloat16).to(DEV)
+    y = rt.fp8_e4m3_gemv_batched(wd, sd, x)
+    torch.cuda.synchronize()
+    assert bool(torch.isfinite(y.float()).all())
+    for t, sc in enumerate(scales):
+        one = rt.fp8_e4m3_gemv(wd, sd, x[t].contiguous()).float()
+        if sc == 0.0:
+            assert bool((y[t] == 0).all())
+            continue
+        d = (one - y[t].float()).abs().max() / one.abs().max()
+        assert float(d) <= 2.0 ** -7, f"scale {sc:g}: {float(d):.3e} from the single call"
+
+
 def test_return_codes(rt, qz):
     from importlib import import_module
     capi = import_module(rt.__name__ + "._capi")
