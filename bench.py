@@ -29,8 +29,8 @@ if ROOT not in sys.path:
 N_EXPERTS, TOP_K, HIDDEN, EXPERT_FF = 256, 6, 4096, 2048
 BYTES_PER_EXPERT = 2 * (EXPERT_FF * HIDDEN // 2 + EXPERT_FF * HIDDEN // 32) + (HIDDEN * EXPERT_FF // 2 + HIDDEN * EXPERT_FF // 32)
 LAYER_BYTES = TOP_K * BYTES_PER_EXPERT + 2 * HIDDEN * 2                 # weights + x + out = 80 232 448
-# dram__bytes_read.sum + dram__bytes_write.sum of one moe_decode_fused_kernel<4096, 2048> launch at this shape
-# (from an ncu capture of that launch on a 64-expert bank: profiles/moe_decode_fused_kernel_decode_batch1.md)
+# dram__bytes_read.sum + dram__bytes_write.sum of one moe_decode_stream_kernel<4096, 2048> launch at this shape,
+# from an ncu capture of that launch on a 64-expert bank (the traffic of a launch does not depend on the bank size)
 FUSED_DRAM_TRAFFIC = 82_430_000
 METRIC = "mxfp4_routed_moe_decode_hbm_throughput"
 UNIT = "GB/s"
@@ -44,7 +44,7 @@ def measured_hbm_peak():
         with open(path) as f:
             return float(json.load(f)["hbm_gbs"]), "measured (MEASURED_PEAKS.json hbm_gbs)"
     except Exception:
-        return 6650.0, "fallback (6.65 TB/s, earlier measurement on this pool)"
+        return 6650.0, "fallback (6.65 TB/s)"
 
 
 def measured_bf16_peak():
@@ -190,7 +190,7 @@ def workload_config(n_gpus: int):
         "bytes_per_step": LAYER_BYTES,
         "l2": "each step picks 6 experts that the previous 8 steps did not use; the bank is 3.42 GB (L2 is 126 MB)",
         "parallelism": "1 GPU" if n_gpus == 1 else f"{n_gpus} replicas (one token and one bank per GPU, no exchange)",
-        "launch": "CUDA graph of up to 500 steps, replayed (--no-graph: direct launches)",
+        "launch": "CUDA graph of up to 500 steps, replayed (--no-graph: direct launches); one decode stream",
     }
 
 
@@ -459,6 +459,107 @@ def dense_configs(rt, qz, torch, dev):
     return out
 
 
+def side_variants(torch, gb, bank, logits, x, out, ws, dev, graph_steps, steps):
+    """Two measurements beside the headline, same bank, same logits, same steps, outside its timed regions:
+    * the FP32-accumulate comparison build of the grouped library (every product and sum of a 32-element block in FP32,
+      the arithmetic of the reference's kernels) - what meeting the reference's precision to the letter would cost;
+    * the reference's own CUDA kernels rebuilt for sm_100a (oracle/_ref, the checker's copy), through their C ABI on
+      the six picked experts stacked, as the reference engine calls them (without its 80 MB gather, which would
+      come on top)."""
+    import ctypes
+    import importlib as _il
+    from ctypes import c_float, c_int, c_void_p
+    res = {}
+    capi = _il.import_module("dsv4_b200.runtime._capi")
+    pkg = sys.modules["dsv4_b200"]
+    E = bank["w1p"].shape[0]
+
+    def timed_graph(call, n_graph, n_steps):
+        stream = torch.cuda.Stream(device=dev)
+        with torch.cuda.stream(stream):
+            for i in range(3):
+                call(i)
+            stream.synchronize()
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g, stream=stream):
+                for i in range(n_graph):
+                    call(i)
+            reps = max(1, n_steps // n_graph)
+            for _ in range(max(1, reps // 2)):
+                g.replay()
+            stream.synchronize()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record(stream)
+            for _ in range(reps):
+                g.replay()
+            b.record(stream)
+            stream.synchronize()
+        return a.elapsed_time(b) * 1e3 / (reps * n_graph)
+
+    # --- FP32-accumulate comparison build
+    path = os.path.join(pkg.LIB_DIR, "libmxfp4_grouped_gemv_f32acc.so")
+    if os.path.exists(path):
+        lib = ctypes.CDLL(path, mode=ctypes.RTLD_LOCAL)
+        restype, argtypes = capi.SIGNATURES["grouped"]["mxfp4_moe_decode_layer"]
+        lib.mxfp4_moe_decode_layer.restype, lib.mxfp4_moe_decode_layer.argtypes = restype, argtypes
+        out32 = torch.empty_like(out)
+        ws32 = torch.empty_like(ws)
+
+        def call32(i, o=out32):
+            rc = lib.mxfp4_moe_decode_layer(
+                capi.ptr(x), capi.ptr(bank["w1p"]), capi.ptr(bank["w3p"]), capi.ptr(bank["w2p"]), capi.ptr(bank["w1s"]),
+                capi.ptr(bank["w3s"]), capi.ptr(bank["w2s"]), capi.ptr(logits[i]), c_int(E), c_int(0), c_float(1e-20),
+                c_float(1.5), c_int(HIDDEN), c_int(EXPERT_FF), c_int(HIDDEN), c_int(TOP_K), capi.ptr(o), capi.ptr(ws32),
+                capi.stream_ptr(dev))
+            if rc != 0:
+                raise RuntimeError(f"f32acc build: mxfp4_moe_decode_layer returned {rc}")
+
+        us = timed_graph(call32, graph_steps, steps)
+        call32(0)
+        gb.moe_decode_layer(bank, logits[0], x, k=TOP_K, score_func="softmax", out=out, workspace=ws, check=False)
+        torch.cuda.synchronize()
+        diff = float((out32.float() - out.float()).abs().max() / out.float().abs().max())
+        res["fp32_accumulate_variant"] = {
+            "us_per_layer": us, "gbs": LAYER_BYTES / us / 1e3,
+            "what": "same kernel built with -DDSV4_FP32_ACCUM: FP32 products and sums inside a block (the reference's arithmetic)",
+            "max_abs_diff_to_product_over_inf_norm": diff}
+    # --- the reference's CUDA kernels
+    try:
+        from oracle import ref_kernels
+        have_ref = ref_kernels.available()
+    except Exception:
+        have_ref = False
+    if have_ref:
+        sets = []
+        g = torch.Generator().manual_seed(SEED)
+        for j in range(3):                                   # three disjoint expert sets: 240 MB > L2 between reuses
+            ids = torch.arange(j * TOP_K, (j + 1) * TOP_K, device=dev)
+            sets.append({k: v[ids].contiguous() for k, v in bank.items()})
+        r = torch.full((TOP_K,), 1.0 / TOP_K, device=dev)
+
+        def ref_call(i):
+            st = sets[i % len(sets)]
+            ref_kernels.grouped_gemv(x, st["w1p"], st["w3p"], st["w2p"], st["w1s"], st["w3s"], st["w2s"], r)
+
+        for i in range(3):
+            ref_call(i)
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        n = 30
+        a.record()
+        for i in range(n):
+            ref_call(i)
+        b.record()
+        torch.cuda.synchronize()
+        us = a.elapsed_time(b) * 1e3 / n
+        res["reference_cuda"] = {
+            "us_per_layer": us, "gbs": LAYER_BYTES / us / 1e3,
+            "what": "the reference's kernel/mxfp4-routed/mxfp4_grouped_gemv.cu compiled unmodified for sm_100a, its "
+                    "mxfp4_grouped_gemv_topk on six stacked experts (memset + 3 kernels), direct launches, three expert "
+                    "sets rotated; without the engine's 80 MB gather in front of it"}
+    return res
+
+
 def run_gpu(args, rank: int, world: int, local_rank: int):
     import torch
     import torch.distributed as dist
@@ -488,13 +589,14 @@ def run_gpu(args, rank: int, world: int, local_rank: int):
     ws = torch.empty(gb.decode_workspace_bytes(TOP_K, EXPERT_FF, HIDDEN), dtype=torch.uint8, device=dev)
 
     def layer(i):
-        # router + FFN in one call: the router runs inside the first of the two kernels
+        # router + FFN in one call: the router runs inside the kernel
         gb.moe_decode_layer(bank, logits[i], x, k=TOP_K, score_func="softmax", out=out, workspace=ws, check=False)
 
-    # one checked call, then capture
-    gb.moe_decode_layer(bank, logits[0], x, k=TOP_K, score_func="softmax", out=out, workspace=ws)
+    # every call of the benchmark is issued from ONE stream, the way a decode loop issues its layers
     stream = torch.cuda.Stream(device=dev)
     with torch.cuda.stream(stream):
+        # one checked call, then capture
+        gb.moe_decode_layer(bank, logits[0], x, k=TOP_K, score_func="softmax", out=out, workspace=ws)
         for i in range(min(3, graph_steps)):
             layer(i)
         stream.synchronize()
@@ -516,26 +618,53 @@ def run_gpu(args, rank: int, world: int, local_rank: int):
         warm_steps = max(args.warmup, 3, MIN_WARMUP_STEPS if not args.no_graph else 3)
         run_steps(warm_steps)
         stream.synchronize()
-        if world > 1:
-            dist.barrier()
-        torch.cuda.synchronize()
+        # the timed region (K steps between a barrier + synchronise on both sides) is run `repeats` times; the
+        # reported time is the median region, the best one is given beside it
         sampler.start()
-        t_start, t_end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        t_start.record(stream)
-        run_steps(args.steps)
-        t_end.record(stream)
-        stream.synchronize()
-        if world > 1:
-            dist.barrier()
-        torch.cuda.synchronize()
-        elapsed_ms = t_start.elapsed_time(t_end)
+        regions_ms = []
+        for _ in range(max(1, args.repeats)):
+            if world > 1:
+                dist.barrier()
+            torch.cuda.synchronize()
+            t_start, t_end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            t_start.record(stream)
+            run_steps(args.steps)
+            t_end.record(stream)
+            stream.synchronize()
+            if world > 1:
+                dist.barrier()
+            torch.cuda.synchronize()
+            regions_ms.append(t_start.elapsed_time(t_end))
         # a short timed region gives the sampler nothing: keep the same load running until it has samples
         t_hold = time.time()
         while len(sampler.samples) < 5 and time.time() - t_hold < 1.5 and sampler._nv is not None:
             graph.replay()
             stream.synchronize()
         clocks = sampler.stop()
-        clocks["sampled"] = "timed region" if elapsed_ms > 200 else "timed region + the same load held for <= 1.5 s"
+        clocks["sampled"] = ("timed regions" if sum(regions_ms) > 200 else
+                             "timed regions + the same load held for <= 1.5 s")
+
+        # parity of the benchmark's own workload, outside the timed regions: step 0 of the 256-expert bank with its
+        # softmax top-6 against the FP32 CPU oracle on the six picked experts (rank 0)
+        parity_check = None
+        if rank == 0 and not args.no_parity:
+            import numpy as np
+            import oracle
+            layer(0)
+            stream.synchronize()
+            ids_d, w_d = gb.decode_picks(ws, TOP_K, EXPERT_FF)
+            ref_ids, ref_w = oracle.route_softmax(logits[0].cpu().numpy()[None], TOP_K)
+            sel = torch.from_numpy(ref_ids[0].astype(np.int64)).to(dev)
+            sub = {n_: v[sel].cpu() for n_, v in bank.items()}
+            ref = oracle.moe_layer_ref(x.cpu()[None], sub, np.arange(TOP_K)[None], ref_w)[0]
+            got = out.float().cpu().numpy()
+            parity_check = {"step": 0, "selection_identical": bool(np.array_equal(ids_d.cpu().numpy(), ref_ids[0])),
+                            "max_abs_over_ref_inf_norm": float(oracle.max_abs_rel(got, ref)),
+                            "cosine": float(oracle.cosine(got, ref)), "tolerance": "1e-2 / 0.9999",
+                            "against": "oracle.moe_layer_ref (CPU, FP32) on the six picked experts"}
+            if not (parity_check["selection_identical"] and parity_check["max_abs_over_ref_inf_norm"] <= 1e-2
+                    and parity_check["cosine"] >= 0.9999):
+                raise RuntimeError(f"the benchmark's own step disagrees with the oracle: {parity_check}")
 
         # end to end through the binding with HOST buffers: every step the host writes that step's x and router
         # logits into one pinned buffer; one captured sequence (H2D copy of the buffer, the layer call, D2H copy of the
@@ -591,6 +720,9 @@ def run_gpu(args, rank: int, world: int, local_rank: int):
 
     if gb.device_status() != 0:
         raise RuntimeError("a kernel gave up on a bounded wait during the benchmark")
+    variants = None
+    if rank == 0 and not args.no_batched:
+        variants = side_variants(torch, gb, bank, logits, x, out, ws, dev, graph_steps, min(args.steps, 2000))
     dense = None
     if n_experts == N_EXPERTS and not args.no_batched and rank == 0:
         dense = dense_configs(rt, qz, torch, dev)
@@ -603,14 +735,16 @@ def run_gpu(args, rank: int, world: int, local_rank: int):
         batched = batched_configs(rt, qz, torch, dist, bank, dev, rank, world)
 
     if world > 1:
-        t = torch.tensor([elapsed_ms, e2e_ms], device=dev, dtype=torch.float64)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        elapsed_ms, e2e_ms = (float(v) for v in t.tolist())
+        t = torch.tensor(regions_ms + [e2e_ms], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)                    # every region: the slowest rank's time
+        vals = [float(v) for v in t.tolist()]
+        regions_ms, e2e_ms = vals[:-1], vals[-1]
+    ordered = sorted(regions_ms)
+    elapsed_ms, best_ms = ordered[len(ordered) // 2], ordered[0]
     if rank != 0:
         if world > 1:
             dist.destroy_process_group()
         return
-
     peak, peak_src = measured_hbm_peak()
     value = world * args.steps * LAYER_BYTES / (elapsed_ms * 1e-3) / 1e9
     e2e_value = world * e2e_steps * LAYER_BYTES / (e2e_ms * 1e-3) / 1e9
@@ -621,23 +755,38 @@ def run_gpu(args, rank: int, world: int, local_rank: int):
     line = {
         "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
         "warmup_steps_run": warm_steps, "ms_per_step": elapsed_ms / args.steps, "us_per_layer": elapsed_ms / args.steps * 1e3,
-        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f16 products, f32 accumulate",
-        "data": "synthetic", "config": dict(workload_config(world), bank_experts=n_experts),
+        "timed_regions": {"repeats": len(regions_ms), "steps_each": args.steps, "value_from": "median region",
+                          "median_us_per_layer": elapsed_ms / args.steps * 1e3, "best_us_per_layer": best_ms / args.steps * 1e3,
+                          "all_us_per_layer": [r / args.steps * 1e3 for r in regions_ms]},
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "f16 products and 16-term f16 partial sums per 32-element block, f32 beyond",
+        "data": "synthetic", "config": workload_config(world), "bank_experts": n_experts,
         "frac_of_hbm_peak": {"of_measured_copy": value / world / peak, "of_nominal_8TBs": value / world / 8000.0},
         "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": HIDDEN * 2 + n_experts * 4,
                 "d2h_bytes_per_step": HIDDEN * 2, "steps": e2e_steps,
                 "us_per_layer": e2e_ms / e2e_steps * 1e3,
                 "what": "host x + logits -> pinned buffer -> device (one copy), router + FFN (one kernel), bf16 out -> pinned host, stream synchronise; every step; the three device operations are one captured launch"},
-        "gpu_launches": args.steps,
-        "kernels_per_step": "1 x moe_decode_fused_kernel<4096,2048> (router + gate/up + grid barrier + down)",
-        "roofline": {"bound": "hbm", "kernel": "moe_decode_fused_kernel<4096, 2048> (the step's only kernel)",
+        "gpu_launches": args.steps * len(regions_ms),
+        "kernels_per_step": "1 x moe_decode_stream_kernel<4096,2048> (router + gate/up + SwiGLU + down + combine)",
+        "roofline": {"bound": "hbm", "kernel": "moe_decode_stream_kernel<4096, 2048> (the step's only kernel)",
                      "achieved": kernel_gbs, "peak": peak, "unit": "GB/s", "frac": kernel_gbs / peak,
                      "traffic": FUSED_DRAM_TRAFFIC, "algorithmic_bytes": LAYER_BYTES, "us_per_launch": launch_us,
                      "peak_source": peak_src},
         "clocks": clocks,
     }
+    if parity_check is not None:
+        line["parity_check"] = parity_check
+    if variants is not None:
+        line.update(variants)
     if batched is not None:
         line["batched"] = batched
+        if world > 1:      # the expert-parallel results of configurations 3 and 4 at this N, with their parity
+            line["ep"] = {name: {"n_gpus": world, "ms": b["ms"], "tflops": b["tflops"], "gbs_min_bytes": b["gbs_min_bytes"],
+                                 "max_abs_vs_1gpu_over_inf_norm": b["max_abs_vs_1gpu_over_inf_norm"],
+                                 "ms_all_to_all_variant": b["ms_all_to_all_variant"],
+                                 "ms_gather_reduce_scatter_variant": b["ms_gather_reduce_scatter_variant"],
+                                 "ms_all_gather_then_peer_combine_variant": b["ms_all_gather_then_peer_combine_variant"]}
+                          for name, b in batched.items()}
     if dense is not None:
         line["dense"] = dense
     if world == 1:
@@ -675,6 +824,8 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-batched", action="store_true", help="skip the batched / expert-parallel side measurements")
     ap.add_argument("--no-graph", action="store_true", help="launch every step directly (profiler captures)")
+    ap.add_argument("--repeats", type=int, default=7, help="timed regions of --steps steps; the median one is reported")
+    ap.add_argument("--no-parity", action="store_true", help="skip the oracle check of the benchmark's own step")
     ap.add_argument("--batched-tokens", type=int, default=0,
                     help="profiler captures: run only the batched layer on this many tokens (uniform routing) and exit")
     ap.add_argument("--experts", type=int, default=N_EXPERTS,

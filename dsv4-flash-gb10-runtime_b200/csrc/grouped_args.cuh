@@ -16,6 +16,10 @@ struct GroupedArgs {
     long long strideAp, strideAs, strideBp, strideBs;   // bytes per expert
     float* mid;                      // [E, H] FP32 SwiGLU intermediate (workspace)
     __nv_bfloat16* out;
+    unsigned long long* mid8;        // single-kernel path: [E, H] {FP32 value, tag} words (same workspace as mid)
+    uint32_t* sync;                  // single-kernel path: generation word (workspace tail)
+    uint32_t spin_limit;             // polls after which a device-side wait gives up
+    int phantom;                     // extra (never arriving) producers to wait for: test of the give-up path only
 };
 
 }  // namespace dsv4

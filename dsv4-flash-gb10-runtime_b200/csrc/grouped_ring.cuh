@@ -23,7 +23,31 @@ constexpr int kRingDownRows = 2;
 constexpr int kRingDownCap = 64;       // output rows per CTA
 constexpr int kRingMaxExperts = 6;     // 2 warps per expert
 
-// 32 E2M1 weights (16 bytes) times 32 activations: two fp16x2 chains of eight, then FP32.
+#ifdef DSV4_FP32_ACCUM
+// Comparison build (-DDSV4_FP32_ACCUM): 32 E2M1 weights times 32 activations with every product and every sum in
+// FP32, the arithmetic of the kernels this library replaces (kernel/mxfp4-routed/mxfp4_grouped_gemv.cu:87-107 of
+// the reference: fmaf over the 32 elements of a block, then the block scale).  About three times the instructions
+// of the fp16 form below; the benchmark times it beside the product.
+__device__ __forceinline__ float fp4_block_dot(const uint4& w, const __half2 (&x)[16]) {
+    const uint32_t word[4] = {w.x, w.y, w.z, w.w};
+    float acc = 0.f;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        __half2 h[4];
+        e2m1x8_to_h2x4(word[i], h);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const float2 wf = __half22float2(h[j]);
+            const float2 xf = __half22float2(x[4 * i + j]);
+            acc = fmaf(wf.x, xf.x, acc);
+            acc = fmaf(wf.y, xf.y, acc);
+        }
+    }
+    return acc;
+}
+#else
+// 32 E2M1 weights (16 bytes) times 32 activations: fp16 products (exact: an E2M1 value times a bf16-precision
+// activation fits fp16's 11 significant bits) summed 16 at a time in two fp16x2 chains, then FP32.
 __device__ __forceinline__ float fp4_block_dot(const uint4& w, const __half2 (&x)[16]) {
     const uint32_t word[4] = {w.x, w.y, w.z, w.w};
     __half2 acc0, acc1;
@@ -44,6 +68,7 @@ __device__ __forceinline__ float fp4_block_dot(const uint4& w, const __half2 (&x
     const float2 f = __half22float2(__hadd2(acc0, acc1));
     return f.x + f.y;
 }
+#endif
 
 // Largest magnitude (as float bits) of 8 consecutive values.
 __device__ __forceinline__ uint32_t amax_bits8(const float (&v)[8]) {

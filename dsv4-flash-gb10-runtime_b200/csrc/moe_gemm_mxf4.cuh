@@ -114,8 +114,11 @@ __global__ void __launch_bounds__(kGemmThreads, 1) moe_gemm_mxf4_kernel(const Mo
     extern __shared__ __align__(1024) uint8_t gemm_smem[];
     __shared__ __align__(8) uint64_t bar_full[S], bar_empty[S], bar_accum, bar_acc_free;
     __shared__ uint32_t tmem_holder;
-    __shared__ int tok_row[2][128];          // activation row of every token of the tile (by tile parity)
-    __shared__ float tok_w[2][128];          // router weight of every token (down)
+    // Token tables, three deep: producers fill the table of tile N + 1 before its barrier while another warp may still
+    // be draining tile N - 1 (the drain runs inside tile N's loop), so two tables are not enough when a tile has
+    // few K steps (hidden <= 1536); a warp cannot get two tiles ahead of another warp's drain.
+    __shared__ int tok_row[3][128];          // activation row of every token of the tile (by tile number mod 3)
+    __shared__ float tok_w[3][128];          // router weight of every token (down)
     __shared__ int s_tiles[kMoeMaxExperts + 1], s_offsets[kMoeMaxExperts + 1];
     pdl_launch_dependents();
 
@@ -158,7 +161,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) moe_gemm_mxf4_kernel(const Mo
             const int quad = warp & 3;
             const int r = quad * 32 + lane;
             const uint32_t trow = tmem + ((uint32_t)(quad * 32) << 16);
-            const float* w_of = tok_w[count & 1];
+            const float* w_of = tok_w[count % 3u];
             auto hand_back = [&]() {
                 // this thread's last read of the accumulator and of the token tables is done
                 tc05_fence_before_sync();
@@ -214,12 +217,12 @@ __global__ void __launch_bounds__(kGemmThreads, 1) moe_gemm_mxf4_kernel(const Mo
         const int drain_at = min(S, n_kb) - 1;        // the stage after whose issue the previous tile is drained
         for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x, ++tile_count) {
             const MoeQTile t = moe_qtile_decode<TOK>(tiles, s_offsets, a.n_experts, m_tiles, tile_rows, a.rows, tile);
-            int* rows_of = tok_row[tile_count & 1];
+            int* rows_of = tok_row[tile_count % 3u];
             if (tid < t.n_valid) {
                 const int slot = t.slot0 + tid;
                 const int pair = a.g.slot_pair[slot];
                 rows_of[tid] = MODE == 0 ? pair / a.k_top : slot;
-                if (MODE == 1) tok_w[tile_count & 1][tid] = a.pair_w[pair];
+                if (MODE == 1) tok_w[tile_count % 3u][tid] = a.pair_w[pair];
             }
             asm volatile("bar.sync 1, %0;" ::"n"(kGemmProducers) : "memory");
 

@@ -7,8 +7,9 @@
 // order, return codes and ownership rules (caller owns all buffers, work is enqueued on the caller's
 // stream, no allocation, no synchronisation).
 //
-// Two kernels, chained by programmatic dependent launch so that the second one can request its first
-// weight rows while the first one drains:
+// At the DSv4 shapes one persistent kernel does the whole call (decode_stream.cuh).  Elsewhere, and on request,
+// two kernels chained by programmatic dependent launch, so that the second one can request its first weight rows
+// while the first one drains:
 //   gate/up kernel : a warp owns a contiguous run of (expert, hidden-row) pairs and streams the W1 and W3
 //                    row of a pair whole (a lane owns up to 4 blocks of the row, the activation vector
 //                    lives in its registers), reduces across lanes and writes silu(g)*u as FP32 into the
@@ -21,7 +22,7 @@
 #include "grouped_args.cuh"
 #include "router.cuh"
 #include "grouped_ring.cuh"
-#include "decode_fused.cuh"
+#include "decode_stream.cuh"
 
 #include <cstdio>
 #include <cstdlib>
@@ -352,70 +353,103 @@ static cudaError_t allow_smem(Kernel kernel, size_t bytes, int (&done)[64]) {
     return err;
 }
 
-// DSV4_B200_FUSED: "0" two chained kernels; "coop" the single kernel launched cooperatively (the runtime guarantees
-// that its 148 CTAs are co-resident: for callers that run grouped calls on several streams of one device); anything
-// else, and the default, the single kernel launched with programmatic stream serialisation (the next layer's CTAs are
-// scheduled while this layer's exit; its own bounded grid barrier relies on no second grid of the kernel being in
-// flight on the device, which a single decode stream guarantees).
+// How the single-kernel path is launched.  Its CTAs wait for one another, so all of them must be resident at once:
+//   1 "coop"  cooperative launch: the runtime guarantees co-residency whatever else runs on the device;
+//   3 "pdl"   programmatic stream serialisation: the next layer's CTAs are scheduled while this layer's exit,
+//             which hides the launch latency; co-residency then rests on the caller running its grouped calls
+//             from ONE stream per device (the reference engine's model).  Calls from several streams may leave
+//             two grids half resident each; their bounded waits then give up (status 3, NaN output).
+//   2 "auto"  (default) the first stream that calls on a device is launched as "pdl", every other stream as
+//             "coop".  Grids of one stream never overlap each other's waits, and a cooperative grid is resident
+//             as a whole, so any mix of streams makes progress: the entry points are safe from any number of
+//             streams and threads, and a single decode stream keeps the faster launch.
+//   0 "0"     no single kernel: the two chained kernels, which wait for nothing.
+// DSV4_B200_FUSED selects the mode; dsv4_b200_set_launch_mode() overrides it at run time.
+static int g_fused_mode = -1;
 static int fused_mode() {
-    static int v = -1;
-    if (v < 0) {
+    if (g_fused_mode < 0) {
         const char* e = std::getenv("DSV4_B200_FUSED");
-        v = (e && e[0] == '0') ? 0 : ((e && e[0] == 'c') ? 1 : 2);
+        int v = 2;
+        if (e && e[0] == '0') v = 0;
+        else if (e && e[0] == 'c') v = 1;
+        else if (e && e[0] == 'p') v = 3;
+        g_fused_mode = v;
     }
-    return v;
+    return g_fused_mode;
+}
+// "auto": the one stream per device that is launched with programmatic stream serialisation.
+static bool owns_pdl(int dev, cudaStream_t stream) {
+    static void* owner[64] = {nullptr};
+    static int have[64] = {0};
+    void* me = reinterpret_cast<void*>(stream);
+    int expected = 0;
+    if (__atomic_compare_exchange_n(&have[dev], &expected, 1, false, __ATOMIC_ACQ_REL, __ATOMIC_ACQUIRE)) {
+        __atomic_store_n(&owner[dev], me, __ATOMIC_RELEASE);
+        __atomic_store_n(&have[dev], 2, __ATOMIC_RELEASE);
+        return true;
+    }
+    while (__atomic_load_n(&have[dev], __ATOMIC_ACQUIRE) != 2) { }     // another thread is writing the owner
+    return __atomic_load_n(&owner[dev], __ATOMIC_ACQUIRE) == me;
 }
 static bool fused_enabled() { return fused_mode() != 0; }
 
-// Single persistent kernel (decode_fused.cuh), one CTA per SM, launched as fused_mode() says.
+// Poll budget of the device-side waits and the phantom producers of the give-up test (dsv4_b200_test_wait_limits).
+static unsigned g_spin_limit = kSpinLimit;
+static int g_phantom = 0;
+
+// Single persistent kernel without a grid barrier (decode_stream.cuh), one CTA per SM, launched as fused_mode() says.
 // Returns 1 when it cannot be used here (the caller then launches the two chained kernels).
 template <int KT, int HT>
-static int grouped_launch_fused(const GroupedArgs& a, cudaStream_t stream, int h_shift, const RouteArgs& rt) {
+static int grouped_launch_stream(GroupedArgs a, cudaStream_t stream, const RouteArgs& rt) {
     static int done[64] = {0};
-    static int coop_ctas[64] = {0};      // resident CTAs per device for this kernel; -1 = cooperative launch unusable
-    using L = FusedLayout<KT, HT>;
-    auto kernel = moe_decode_fused_kernel<KT, HT>;
+    static int usable[64] = {0};         // 1 = yes, -1 = no
+    using L = StreamLayout<KT, HT>;
+    auto kernel = moe_decode_stream_kernel<KT, HT>;
+    constexpr int kThreads = kStreamThreads;
     int dev = 0;
-    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 1;
-    if (coop_ctas[dev] == 0) {
+    if (a.sync == nullptr || cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 1;
+    if (usable[dev] == 0) {
         int coop = 0, per_sm = 0;
         cudaDeviceGetAttribute(&coop, cudaDevAttrCooperativeLaunch, dev);
         if (allow_smem(kernel, L::kBytes, done) != cudaSuccess || !coop ||
-            cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, kFusedWarps * 32, L::kBytes) != cudaSuccess ||
+            cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, kThreads, L::kBytes) != cudaSuccess ||
             per_sm < 1) {
             cudaGetLastError();
-            coop_ctas[dev] = -1;
+            usable[dev] = -1;
         } else {
-            coop_ctas[dev] = sm_count();     // one CTA per SM
+            usable[dev] = 1;
         }
     }
-    if (coop_ctas[dev] < 0) return 1;
-    long long grid = coop_ctas[dev];
-    const long long pairs = (long long)a.E * a.H;
-    if (grid > pairs) grid = pairs;
+    if (usable[dev] < 0) return 1;
+    long long grid = sm_count();         // one CTA per SM
+    if (grid > kStreamMaxGrid) grid = kStreamMaxGrid;
     if (grid > a.O) grid = a.O;
-    if ((long long)kFusedCap * grid < a.O) return 1;                 // too many output rows per CTA
+    if (grid > HT) grid = HT;
+    if ((long long)kStreamCap * grid < a.O || (long long)kStreamCapA * grid < HT || a.E > kStreamMaxExperts) return 1;
+    a.spin_limit = g_spin_limit;
+    a.mid8 = reinterpret_cast<unsigned long long*>(a.mid);
+    a.phantom = g_phantom;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3((unsigned)grid);
-    cfg.blockDim = dim3(kFusedWarps * 32);
+    cfg.blockDim = dim3(kThreads);
     cfg.dynamicSmemBytes = L::kBytes;
     cfg.stream = stream;
     // a cooperative launch is not combined with programmatic stream serialisation: one or the other
-    const bool own_barrier = fused_mode() == 2;      // (launch attribute only: the kernel is the same)
     cudaLaunchAttribute attr[1];
-    if (own_barrier) {
-        attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-        attr[0].val.programmaticStreamSerializationAllowed = 1;
-    } else {
+    const int mode = fused_mode();
+    if (mode == 1 || (mode == 2 && !owns_pdl(dev, stream))) {
         attr[0].id = cudaLaunchAttributeCooperative;
         attr[0].val.cooperative = 1;
+    } else {
+        attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[0].val.programmaticStreamSerializationAllowed = 1;
     }
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    const cudaError_t err = cudaLaunchKernelEx(&cfg, kernel, a, h_shift, rt);
+    const cudaError_t err = cudaLaunchKernelEx(&cfg, kernel, a, rt);
     if (err != cudaSuccess) {
         cudaGetLastError();
-        coop_ctas[dev] = -1;                                         // do not try again on this device
+        usable[dev] = -1;                                            // do not try again on this device
         return 1;
     }
     return 0;
@@ -470,7 +504,7 @@ static int grouped_try_ring(const GroupedArgs& a, cudaStream_t stream, const cha
     while ((1 << h_shift) < a.H) ++h_shift;
 #define DSV4_RING(KT, HT)                                                                          \
     if (a.K == KT && a.H == HT) {                                                                  \
-        if (stages == 3 && fused_enabled() && grouped_launch_fused<KT, HT>(a, stream, h_shift, rt) == 0) return 0; \
+        if (stages == 3 && fused_enabled() && grouped_launch_stream<KT, HT>(a, stream, rt) == 0) return 0; \
         return grouped_launch_ring<KT, HT>(a, stream, who, h_shift, stages, rt);                  \
     }
     DSV4_RING(4096, 2048) DSV4_RING(4096, 1024) DSV4_RING(2048, 2048) DSV4_RING(2048, 1024)
@@ -543,6 +577,13 @@ static int check_shape(const char* who, int K_in, int hidden, int out_dim) {
     return 0;
 }
 
+// Workspace layout: [n_exp * hidden * 8 bytes: the intermediate - FP32 values for the two-kernel chain, 8-byte
+// {value, tag} words for the single kernel][`extra` bytes of other per-call results][64 bytes: generation word].
+static uint32_t* sync_area(void* workspace, int n_exp, int hidden, size_t extra) {
+    return reinterpret_cast<uint32_t*>(reinterpret_cast<uint8_t*>(workspace) +
+                                       (size_t)n_exp * (size_t)hidden * 8 + extra);
+}
+
 static bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
 }  // namespace dsv4
@@ -577,15 +618,17 @@ DSV4_API int mxfp4_grouped_gemv_topk(const __nv_bfloat16* x, const uint8_t* W1_p
     a.strideBp = (long long)out_dim * (hidden / 2); a.strideBs = (long long)out_dim * (hidden / 32);
     a.mid = reinterpret_cast<float*>(workspace);
     a.out = out;
+    a.sync = sync_area(workspace, n_exp, hidden, 0);
     return grouped_forward(a, stream, who);
 }
 
 // Replaces kernel/mxfp4-routed/mxfp4_grouped_gemv.cu:406-409.  The intermediate is kept in FP32 here
-// (n_exp * hidden * 4 bytes); callers size their buffer through this query, as the reference's callers do.
+// (n_exp * hidden * 4 bytes) and is followed by the readiness flags of the single-kernel path; callers size their
+// buffer through this query, as the reference's callers do.
 DSV4_API size_t mxfp4_grouped_workspace_bytes(int n_exp, int hidden, int out_dim) {
     (void)out_dim;
     if (n_exp <= 0 || hidden <= 0) return 0;
-    return (size_t)n_exp * (size_t)hidden * sizeof(float);
+    return (size_t)n_exp * (size_t)hidden * 8 + kStreamSyncBytes;
 }
 
 // Additive: same computation, but the experts are picked from a resident bank by index, so the caller
@@ -617,6 +660,7 @@ static int grouped_ids_impl(const char* who, int stages, const __nv_bfloat16* x,
     a.strideBp = (long long)out_dim * (hidden / 2); a.strideBs = (long long)out_dim * (hidden / 32);
     a.mid = reinterpret_cast<float*>(workspace);
     a.out = out;
+    a.sync = sync_area(workspace, n_exp, hidden, 0);
     return grouped_forward(a, stream, who, stages);
 }
 
@@ -685,11 +729,11 @@ DSV4_API int mxfp4_moe_route_topk(const float* logits, int n_tokens, int n_exper
 // (K_in in {1024, 2048, 4096}, hidden in {1024, 2048}, n_experts <= 256, k <= 6) the router runs inside the first
 // kernel; otherwise a router kernel is launched first.  The picks and their weights are left in the workspace
 // (see mxfp4_moe_decode_workspace_bytes) where the caller may read them after the call: int32 ids at byte offset
-// k * hidden * 4, FP32 weights 32 bytes further.
+// k * hidden * 8, FP32 weights 32 bytes further.
 DSV4_API size_t mxfp4_moe_decode_workspace_bytes(int k, int hidden, int out_dim) {
     (void)out_dim;
     if (k <= 0 || hidden <= 0) return 0;
-    return (size_t)k * (size_t)hidden * sizeof(float) + 64;
+    return (size_t)k * (size_t)hidden * 8 + 64 + kStreamSyncBytes;
 }
 
 DSV4_API int mxfp4_moe_decode_layer(const __nv_bfloat16* x, const uint8_t* bank_W1_packed,
@@ -714,8 +758,8 @@ DSV4_API int mxfp4_moe_decode_layer(const __nv_bfloat16* x, const uint8_t* bank_
     RouteArgs rt;
     rt.logits = logits; rt.n_experts = n_experts; rt.k = k; rt.score_func = score_func; rt.eps = eps;
     rt.scaling = scaling;
-    rt.ids_out = reinterpret_cast<int*>(ws + (size_t)k * hidden * sizeof(float));
-    rt.w_out = reinterpret_cast<float*>(ws + (size_t)k * hidden * sizeof(float) + 32);
+    rt.ids_out = reinterpret_cast<int*>(ws + (size_t)k * hidden * 8);
+    rt.w_out = reinterpret_cast<float*>(ws + (size_t)k * hidden * 8 + 32);
     GroupedArgs a;
     a.x = x; a.w1p = bank_W1_packed; a.w3p = bank_W3_packed; a.w2p = bank_W2_packed;
     a.w1s = bank_W1_scale; a.w3s = bank_W3_scale; a.w2s = bank_W2_scale;
@@ -724,6 +768,7 @@ DSV4_API int mxfp4_moe_decode_layer(const __nv_bfloat16* x, const uint8_t* bank_
     a.strideBp = (long long)out_dim * (hidden / 2); a.strideBs = (long long)out_dim * (hidden / 32);
     a.mid = reinterpret_cast<float*>(workspace);
     a.out = out;
+    a.sync = sync_area(workspace, k, hidden, 64);
     if (n_experts <= 256) {
         a.r = nullptr; a.ids = nullptr;                  // both come from the fused router
         if (int rc = grouped_try_ring(a, stream, who, 3, rt); rc != 1) return rc;
@@ -749,18 +794,37 @@ DSV4_API int mxfp4_dequant_bf16(const uint8_t* packed, const uint8_t* scale, lon
 }
 
 // Added (diagnostic): 0 unless a kernel of this library gave up on a bounded wait since the last call
-// (1 = gate/up ring, 2 = down ring); the status is cleared by the call.  Synchronises the device.
+// (1 = a gate/up row or its scales never landed, 2 = a down row or its scales, 3 = an expert's intermediate never
+// became complete); the status is cleared by the call.  Synchronises the device.
 DSV4_API int dsv4_b200_device_status(void) {
     int v = 0, zero = 0;
     if (cudaMemcpyFromSymbol(&v, g_device_status, sizeof(int)) != cudaSuccess) return -1;
-    if (v != 0) {
-        cudaMemcpyToSymbol(g_device_status, &zero, sizeof(int));
-        // a grid barrier that gave up leaves its words out of step: start again from zero
-        cudaMemcpyToSymbol(g_fused_count, &zero, sizeof(int));
-        cudaMemcpyToSymbol(g_fused_base, &zero, sizeof(int));
-        cudaMemcpyToSymbol(g_fused_exits, &zero, sizeof(int));
-    }
+    // (nothing else to re-arm: what the single-kernel path waits on lives in the caller's workspace and is
+    // re-tagged by every launch)
+    if (v != 0) cudaMemcpyToSymbol(g_device_status, &zero, sizeof(int));
     return v;
+}
+
+// Added (no counterpart): how the single-kernel path is launched from now on in this process.
+// 0 = two chained kernels, 1 = cooperative launch, 2 = automatic (first stream of a device programmatic, the others
+// cooperative; the default), 3 = programmatic stream serialisation for every stream; see fused_mode().
+// Returns the previous mode, or -1 for a value outside 0..3 (nothing changes).
+DSV4_API int dsv4_b200_set_launch_mode(int mode) {
+    const int before = fused_mode();
+    if (mode < 0 || mode > 3) return -1;
+    g_fused_mode = mode;
+    return before;
+}
+
+// Added (test hook, no counterpart): poll budget of the device-side waits of the single-kernel path, and a number of
+// producers that never arrive.  With phantom_ctas > 0 the next calls wait for readiness flags nobody publishes, give
+// up after `polls` polls (microseconds for a few thousand), record status 3 and write NaN - without a fault, a
+// trap or an unbounded loop.  (0, 0) restores the defaults.  Returns -1 for negative arguments.
+DSV4_API int dsv4_b200_test_wait_limits(long long polls, int phantom_ctas) {
+    if (polls < 0 || phantom_ctas < 0 || phantom_ctas > 64) return -1;
+    g_spin_limit = polls == 0 ? kSpinLimit : (unsigned)(polls > 0xffffffffLL ? 0xffffffffLL : polls);
+    g_phantom = phantom_ctas;
+    return 0;
 }
 
 // ------------------------------------------------------------------------------------------------
@@ -769,11 +833,12 @@ DSV4_API int dsv4_b200_device_status(void) {
 // Some hosts cannot hand this library a scratch buffer at call time: an engine that gave all free HBM to its
 // expert bank and KV cache at start-up has nothing left to carve a workspace from, and a decode thread must not
 // enter cudaMalloc because that call synchronises the whole device.  For them the SwiGLU intermediate lives in
-// this fixed array inside the library image.  Every GPU that loads the library carries these 96 KB until the
+// this fixed array inside the library image.  Every GPU that loads the library carries these 192 KB until the
 // process exits.
 constexpr int kStaticMaxExperts = 6;
 constexpr int kStaticMaxHidden = 4096;
-static __device__ __align__(256) unsigned char g_static_scratch[kStaticMaxExperts * kStaticMaxHidden * sizeof(float)];
+static __device__ __align__(256) unsigned char
+    g_static_scratch[kStaticMaxExperts * kStaticMaxHidden * 8 + kStreamSyncBytes];
 
 // Device address of g_static_scratch on the current device, or nullptr (with a message) if the runtime refuses.
 // In host code the array's name is only a handle for the runtime, not an address a kernel could use, so the
@@ -813,6 +878,7 @@ DSV4_API int mxfp4_grouped_gemv_topk_static(const __nv_bfloat16* x, const uint8_
                                             const uint8_t* W2_scale, const float* rweights, int K_in, int hidden,
                                             int out_dim, int n_exp, __nv_bfloat16* out, cudaStream_t stream) {
     const char* who = "mxfp4_grouped_gemv_topk_static";
+    // beyond what the built-in array holds: -10; a supported size but not the six experts of the workspace entry: -4
     if (hidden > kStaticMaxHidden || n_exp > kStaticMaxExperts) {
         std::fprintf(stderr, "%s: n_exp=%d hidden=%d exceed the built-in scratch (%d experts x %d)\n", who, n_exp,
                      hidden, kStaticMaxExperts, kStaticMaxHidden);
@@ -838,5 +904,6 @@ DSV4_API int mxfp4_grouped_gemv_topk_static(const __nv_bfloat16* x, const uint8_
     a.strideBp = (long long)out_dim * (hidden / 2); a.strideBs = (long long)out_dim * (hidden / 32);
     a.mid = reinterpret_cast<float*>(scratch);
     a.out = out;
+    a.sync = sync_area(scratch, n_exp, hidden, 0);
     return grouped_forward(a, stream, who);
 }

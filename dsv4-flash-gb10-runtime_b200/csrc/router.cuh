@@ -55,26 +55,45 @@ __device__ __forceinline__ void route_token(const float* __restrict__ row, int n
     }
     float my_score = 0.f, sum = 0.f;
     id = -1;
-    for (int j = 0; j < k; ++j) {
-        uint32_t best = 0;
-        int best_i = 0;
+    // the lane's best key and where it sits: recomputed only by the lane that has just given a pick away
+    uint32_t best = 0;
+    int best_i = 0;
 #pragma unroll
-        for (int i = 0; i < PL; ++i)
-            if (key[i] > best) { best = key[i]; best_i = i; }             // strict: lowest index wins in a lane
+    for (int i = 0; i < PL; ++i)
+        if (key[i] > best) { best = key[i]; best_i = i; }                 // strict: lowest index wins in a lane
+    for (int j = 0; j < k; ++j) {
         const uint32_t top = __reduce_max_sync(kFullMask, best);
         const int cand = (best == top && top != 0u) ? best_i * 32 + lane : 0x7fffffff;
-        const int win = __reduce_min_sync(kFullMask, cand);
+        // the lane holding it: a vote; only an exact tie between lanes needs a second reduction (lowest index wins)
+        const uint32_t holders = __ballot_sync(kFullMask, cand != 0x7fffffff);
+        int win = 0x7fffffff;
+        if (holders != 0u)
+            win = (holders & (holders - 1u)) == 0u ? __shfl_sync(kFullMask, cand, __ffs(holders) - 1)
+                                                   : __reduce_min_sync(kFullMask, cand);
         const uint32_t bits = (top >> 31) ? (top ^ 0x80000000u) : ~top;
         const float best_score = top != 0u ? __uint_as_float(bits) : -INFINITY;
         if (lane == j) { my_score = best_score; id = win != 0x7fffffff ? win : 0; }
-        if ((win & 31) == lane && win != 0x7fffffff) {
+        if (cand == win && win != 0x7fffffff) {
+            best = 0;
+#pragma unroll
+            for (int i = 0; i < PL; ++i) {
+                if (i == best_i) key[i] = 0u;
+            }
+            best_i = 0;
 #pragma unroll
             for (int i = 0; i < PL; ++i)
-                if (i == (win >> 5)) key[i] = 0u;
+                if (key[i] > best) { best = key[i]; best_i = i; }
         }
-        sum += score_func == 0 ? __expf(best_score - row_max) : best_score;
     }
-    w = score_func == 0 ? __expf(my_score - row_max) / sum : my_score / (sum + eps) * scaling;
+    // the weights need the picks only: one exponential per lane instead of one per round
+    {
+        const float mine = lane < k ? (score_func == 0 ? __expf(my_score - row_max) : my_score) : 0.f;
+        sum = mine;
+#pragma unroll
+        for (int off = 16; off > 0; off >>= 1) sum += __shfl_xor_sync(kFullMask, sum, off);
+        my_score = mine;
+    }
+    w = score_func == 0 ? my_score / sum : my_score / (sum + eps) * scaling;
 }
 
 }  // namespace dsv4

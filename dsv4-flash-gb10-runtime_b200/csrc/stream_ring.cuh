@@ -62,6 +62,16 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity,
     return false;
 }
 
+// The same with the poll budget given at run time; code 0 records nothing.
+__device__ __forceinline__ bool mbar_wait_limit(uint32_t bar, uint32_t parity, int code, uint32_t limit) {
+    for (uint32_t it = 0; it < limit; ++it) {
+        if (mbar_try_wait(bar, parity)) return true;   // try_wait itself parks the thread for a short while
+        if (it > 64) __nanosleep(64);
+    }
+    if (code != 0) atomicExch(&g_device_status, code);
+    return false;
+}
+
 // Global -> this CTA's shared memory, completion counted in bytes on `bar`.
 // Both addresses 16-byte aligned, size a multiple of 16.
 __device__ __forceinline__ void bulk_copy_g2s(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {

@@ -22,6 +22,8 @@ SIGNATURES = {
         "mxfp4_moe_route_topk": (c_int, [_P, c_int, c_int, c_int, c_int, c_float, c_float, _P, _P, _P]),
         "mxfp4_dequant_bf16": (c_int, [_P, _P, c_longlong, c_int, _P, _P]),
         "dsv4_b200_device_status": (c_int, []),
+        "dsv4_b200_set_launch_mode": (c_int, [c_int]),
+        "dsv4_b200_test_wait_limits": (c_int, [c_longlong, c_int]),
     },
     "mxfp4": {
         "mxfp4_gemv_m1": (c_int, [_P, _P, _P, c_int, c_int, c_int64, c_int64, _P, _P]),

@@ -206,7 +206,7 @@ def decode_workspace_bytes(k: int, hidden: int, out_dim: int) -> int:
 
 def decode_picks(workspace: torch.Tensor, k: int, hidden: int):
     """(ids int32 [k], weights float32 [k]) left in the workspace by moe_decode_layer."""
-    off = k * hidden * 4
+    off = k * hidden * 8
     return workspace[off:off + 4 * k].view(torch.int32), workspace[off + 32:off + 32 + 4 * k].view(torch.float32)
 
 
@@ -232,5 +232,24 @@ def device_status() -> int:
     return int(_capi.load("grouped").dsv4_b200_device_status())
 
 
-__all__ = ["device_status", "moe_decode_layer", "decode_workspace_bytes", "decode_picks", "mxfp4_grouped_gemv", "mxfp4_grouped_gemv_static", "mxfp4_grouped_gemv_ids", "moe_route_topk", "mxfp4_dequant_bf16",
+LAUNCH_MODES = {"chain": 0, "coop": 1, "auto": 2, "pdl": 3}
+
+
+def set_launch_mode(mode: str) -> str:
+    """How the single-kernel decode path is launched from now on: "auto" (default: the first stream that calls on a
+    device with programmatic stream serialisation, every other stream cooperatively - safe from any number of
+    streams), "pdl" (programmatic for every stream: only for callers with one stream per device), "coop"
+    (cooperative for every stream) or "chain" (two kernels).  Returns the previous mode."""
+    before = int(_capi.load("grouped").dsv4_b200_set_launch_mode(c_int(LAUNCH_MODES[mode])))
+    return {v: k for k, v in LAUNCH_MODES.items()}.get(before, str(before))
+
+
+def debug_wait_limits(polls: int, phantom_ctas: int) -> None:
+    """Test hook: poll budget of the device-side waits and a number of producers that never arrive; (0, 0) restores
+    the defaults."""
+    if _capi.load("grouped").dsv4_b200_test_wait_limits(c_longlong(polls), c_int(phantom_ctas)) != 0:
+        raise ValueError("bad wait limits")
+
+
+__all__ = ["device_status", "set_launch_mode", "debug_wait_limits", "moe_decode_layer", "decode_workspace_bytes", "decode_picks", "mxfp4_grouped_gemv", "mxfp4_grouped_gemv_static", "mxfp4_grouped_gemv_ids", "moe_route_topk", "mxfp4_dequant_bf16",
            "workspace_bytes", "MXFP4_BLOCK_ELEMS"]

@@ -51,7 +51,9 @@ def test_workspace_bytes(pkg):
     import importlib
     capi = importlib.import_module("dsv4_b200.runtime._capi")
     lib = capi.load("grouped")
-    assert lib.mxfp4_grouped_workspace_bytes(6, 2048, 4096) == 6 * 2048 * 4
+    # the intermediate [n_exp, hidden] as 8-byte {value, tag} words, then the generation word
+    assert lib.mxfp4_grouped_workspace_bytes(6, 2048, 4096) == 6 * 2048 * 8 + 64
+    assert lib.mxfp4_moe_decode_workspace_bytes(6, 2048, 4096) == 6 * 2048 * 8 + 64 + 64
     assert lib.mxfp4_grouped_workspace_bytes(0, 2048, 4096) == 0
 
 

@@ -1,6 +1,7 @@
-"""The decode layer under its three launch modes (environment switch read once per process, hence child processes):
-the single kernel launched with programmatic stream serialisation (default), the same kernel launched
-cooperatively, and the two-kernel chain.  Each child checks the layer against the CPU oracle and against a repeat call (bitwise)."""
+"""The decode layer under its launch modes (environment switch read once per process, hence child processes): the
+single kernel launched automatically (default: programmatic stream serialisation for the first stream of a device,
+cooperative for any other), programmatically for every stream, cooperatively for every stream, and the two-kernel
+chain.  Each child checks the layer against the CPU oracle and against a repeat call (bitwise)."""
 import os
 import subprocess
 import sys
@@ -26,7 +27,7 @@ bank = qz.make_expert_bank(E, K, H, "cpu", seed=11)
 dbank = {{n: v.to(dev) for n, v in bank.items()}}
 g = torch.Generator().manual_seed(5)
 worst = 0.0
-for step in range(6):                      # several layers back to back: the grid barrier's words carry over
+for step in range(6):                      # several layers back to back
     x = torch.randn(K, generator=g).to(torch.bfloat16)
     logits = torch.randn(E, generator=g)
     out = gb.moe_decode_layer(dbank, logits.to(dev), x.to(dev), k=k, score_func="softmax")
@@ -44,7 +45,7 @@ print("ok", worst)
 """
 
 
-@pytest.mark.parametrize("mode", ["coop", "pdl", "0"])
+@pytest.mark.parametrize("mode", ["auto", "coop", "pdl", "0"])
 def test_decode_layer_launch_modes(mode):
     env = dict(os.environ, DSV4_B200_FUSED=mode)
     r = subprocess.run([sys.executable, "-c", CHILD.format(root=ROOT)], env=env, capture_output=True, text=True,

@@ -107,3 +107,66 @@ def test_moe_forward_skips_negative_ids(rt, qz, path):
     err, cos = oracle.max_abs_rel(got, ref), oracle.cosine(got, ref)
     assert err <= 1e-2 and cos >= 0.9999, f"max-abs/inf {err:.3e} cosine {cos:.7f}"
     assert not np.any(got[5])
+
+
+def test_moe_forward_short_reduction_many_tiles(rt, qz):
+    """hidden = 1024 (four 256-wide K steps per down tile) with several tiles per CTA: the token tables of three
+    consecutive tiles are live at once in the block-scaled kernel."""
+    dev = torch.device("cuda:0")
+    T, E, K, H, O, k = 2048, 8, 512, 1024, 2048, 2
+    bank = qz.make_expert_bank(E, K, H, "cpu", seed=31)
+    g = torch.Generator().manual_seed(32)
+    w2 = (torch.randn(E, O, H, generator=g) * 0.02).to(torch.bfloat16)
+    bank["w2p"], bank["w2s"] = qz.quantize_mxfp4(w2)
+    x = torch.randn(T, K, generator=g).to(torch.bfloat16)
+    ids, w = routing(T, E, k, seed=33)
+    w = w * torch.linspace(0.25, 4.0, T)[:, None]            # router weights that differ a lot from tile to tile
+    dbank = {n: v.to(dev) for n, v in bank.items()}
+    ref = oracle.moe_layer_ref(x, bank, ids.numpy(), w.numpy())
+    for path in ("mxf4", "fp16"):
+        for rep in range(3):
+            out = rt.moe_forward(dbank, x.to(dev), ids.to(dev), w.to(dev), path=path)
+            torch.cuda.synchronize()
+            got = out.float().cpu().numpy()
+            err, cos = oracle.max_abs_rel(got, ref), oracle.cosine(got, ref)
+            assert err <= 1e-2 and cos >= 0.9999, f"{path} rep {rep}: max-abs/inf {err:.3e} cosine {cos:.7f}"
+    assert rt.moe_device_status() == 0
+
+
+@pytest.fixture(scope="module")
+def full_bank(qz):
+    dev = torch.device("cuda:0")
+    bank = qz.make_expert_bank(256, 4096, 2048, dev, seed=1236, chunk=16)
+    yield bank
+    del bank
+    torch.cuda.empty_cache()
+
+
+@pytest.mark.parametrize("name,T,zipf,seed,n_sample", [("config3_decode_batch64_zipf", 64, True, 1237, 12),
+                                                      ("config4_prefill_4096_uniform", 4096, False, 1238, 24)])
+def test_configs_3_and_4_at_stated_size_against_the_oracle(rt, full_bank, name, T, zipf, seed, n_sample):
+    """The batched configurations as stated (256 experts, K = 4096, hidden = 2048, top-6; 64 tokens with Zipf(1.1)
+    routing, 4096 tokens with uniform routing) through the batched layer, a sample of tokens checked against the FP32
+    CPU oracle (only the experts those tokens use are dequantised on the CPU)."""
+    dev = torch.device("cuda:0")
+    E, K, k = 256, 4096, 6
+    g = torch.Generator().manual_seed(seed)
+    if zipf:
+        p = 1.0 / torch.arange(1, E + 1, dtype=torch.float64) ** 1.1
+        ids = torch.multinomial(p.expand(T, E), k, replacement=False, generator=g)
+    else:
+        ids = torch.rand(T, E, generator=g).topk(k).indices
+    w = torch.softmax(torch.randn(T, k, generator=g), -1).float()
+    x = torch.randn(T, K, generator=g).to(torch.bfloat16)
+    out = rt.moe_forward(full_bank, x.to(dev), ids.to(torch.int32).to(dev), w.to(dev))
+    torch.cuda.synchronize()
+    assert rt.moe_device_status() == 0
+    sample = torch.randperm(T, generator=g)[:n_sample].sort().values
+    used = torch.unique(ids[sample])
+    remap = {int(e): i for i, e in enumerate(used.tolist())}
+    sub = {n: v[used.to(dev)].cpu() for n, v in full_bank.items()}
+    ids_s = np.vectorize(remap.get)(ids[sample].numpy())
+    ref = oracle.moe_layer_ref(x[sample], sub, ids_s, w[sample].numpy())
+    got = out[sample.to(dev)].float().cpu().numpy()
+    err, cos = oracle.max_abs_rel(got, ref), oracle.cosine(got, ref)
+    assert err <= 1e-2 and cos >= 0.9999, f"{name}: max-abs/inf {err:.3e} cosine {cos:.7f}"
