@@ -10,8 +10,10 @@
  * Conventions, identical to the reference: every pointer is DEVICE memory owned by the caller; nothing is
  * allocated, freed or retained; work is enqueued on `stream` and the call returns without synchronising;
  * the return value is 0 on success and negative on a rejected argument or a failed launch (message on stderr);
- * outputs are fully overwritten; workspace contents are undefined afterwards.  The entry points are
- * re-entrant; concurrent calls need distinct workspaces.  `stream` is a cudaStream_t passed as void*.
+ * outputs are fully overwritten; workspace contents are undefined afterwards and need no initialisation.  The entry
+ * points keep no state of a call in the library: they are re-entrant, and calls from any number of streams and host
+ * threads may overlap on a device as long as each has its own workspace (the kernels of the grouped entries wait on
+ * words inside that workspace only).  `stream` is a cudaStream_t passed as void*.
  * bf16 values are passed as uint16_t bit patterns (= __nv_bfloat16).
  *
  * Alignment: x, the packed-weight bases and the workspace of the grouped entry must be 16-byte aligned
@@ -36,7 +38,9 @@ extern "C" {
  * scale [n_exp, out_dim, hidden/32].  Packed bytes hold two E2M1 values (low nibble = even index), scales are
  * E8M0 bytes (2^(b-127); 0xFF contributes 0).
  * Returns -1 K_in % 32, -2 hidden % 32, -3 K_in or hidden > 4096, -4 n_exp != 6, -5/-6 launch failure (as the
- * reference), -8 null / misaligned pointer or out_dim <= 0. */
+ * reference), -8 null / misaligned pointer or out_dim <= 0.
+ * workspace: mxfp4_grouped_workspace_bytes() bytes (n_exp * hidden * 8 + 64 here, against the reference's
+ * n_exp * hidden * 2 + out_dim * 4: callers size it through the query, as the reference's callers do). */
 int mxfp4_grouped_gemv_topk(const uint16_t* x, const uint8_t* W1_packed, const uint8_t* W3_packed,
                             const uint8_t* W2_packed, const uint8_t* W1_scale, const uint8_t* W3_scale,
                             const uint8_t* W2_scale, const float* rweights, int K_in, int hidden, int out_dim,
@@ -44,7 +48,7 @@ int mxfp4_grouped_gemv_topk(const uint16_t* x, const uint8_t* W1_packed, const u
 
 /* Has no counterpart in the reference.  mxfp4_grouped_gemv_topk for hosts that cannot supply a workspace at call
  * time (all free HBM already given to the expert bank and KV cache, or a decode thread that must stay out of
- * cudaMalloc because it synchronises the device): the FP32 intermediate lives in a 96 KB array inside the library
+ * cudaMalloc because it synchronises the device): the intermediate lives in a 192 KB array inside the library
  * image, present on every GPU that loads the library.  Allocates and frees nothing.  Limits: n_exp == 6,
  * hidden <= 4096 (-10 beyond that).  The first call on a device fetches the array's address: make it before any
  * stream capture on that device.  All calls on a device share the array, so calls whose kernels overlap on the GPU
@@ -84,9 +88,9 @@ int mxfp4_moe_route_topk(const float* logits, int n_tokens, int n_experts, int k
 
 /* Added (no counterpart; the whole of kernel/cpp-engine-mxfp4/routed.cu:373-503 for one token in one call): router
  * + routed-expert FFN over a resident bank.  logits FP32 [n_experts]; k experts per token.  At K_in in {1024, 2048,
- * 4096}, hidden in {1024, 2048}, n_experts <= 256, k <= 6 the router runs inside the first kernel (2 launches),
+ * 4096}, hidden in {1024, 2048}, n_experts <= 256, k <= 6 the whole layer is ONE kernel launch (router inside),
  * otherwise a router kernel is launched first (3 launches).  After the call the workspace holds the picks: int32 ids
- * at byte offset k * hidden * 4, FP32 weights 32 bytes further.  Return codes as mxfp4_grouped_gemv_topk_ids. */
+ * at byte offset k * hidden * 8, FP32 weights 32 bytes further.  Return codes as mxfp4_grouped_gemv_topk_ids. */
 int mxfp4_moe_decode_layer(const uint16_t* x, const uint8_t* bank_W1_packed, const uint8_t* bank_W3_packed,
                            const uint8_t* bank_W2_packed, const uint8_t* bank_W1_scale, const uint8_t* bank_W3_scale,
                            const uint8_t* bank_W2_scale, const float* logits, int n_experts, int score_func, float eps,
@@ -99,8 +103,26 @@ int mxfp4_dequant_bf16(const uint8_t* packed, const uint8_t* scale, long long ro
                        void* stream);
 
 /* Added (diagnostic, no counterpart): 0 unless a kernel of this library gave up on one of its bounded waits since
- * the last call (1 = gate/up stage, 2 = down stage); clears the status.  Synchronises the device. */
+ * the last call (1 = a gate/up row never landed, 2 = a down row, 3 = an expert's intermediate never became complete);
+ * clears the status.  A kernel that gives up writes NaN to its output rows, so the damage is also visible downstream.
+ * Synchronises the device. */
 int dsv4_b200_device_status(void);
+
+/* Added (no counterpart): how the single-kernel path of the grouped entries is launched from now on in this process.
+ * Its CTAs wait for one another's results, so all of them must be resident together:
+ *   2 automatic (default): the first stream that calls on a device gets programmatic stream serialisation (the next
+ *     layer's CTAs are scheduled while this layer's exit), every other stream a cooperative launch (co-residency
+ *     guaranteed by the runtime) - any mix of streams makes progress;
+ *   1 cooperative for every stream;  3 programmatic for every stream (only for callers with ONE stream per device);
+ *   0 two chained kernels that wait for nothing.
+ * The environment variable DSV4_B200_FUSED (auto | coop | pdl | 0) sets the initial mode.  Returns the previous mode,
+ * -1 for another value. */
+int dsv4_b200_set_launch_mode(int mode);
+
+/* Added (test hook, no counterpart): poll budget of the device-side waits of the single-kernel path, and a number of
+ * producers that never arrive (> 0: the next calls wait for data nobody writes, give up after `polls` polls, record
+ * status 3 and write NaN - nothing faults or spins without a limit).  (0, 0) restores the defaults. */
+int dsv4_b200_test_wait_limits(long long polls, int phantom_ctas);
 
 /* ---- libmxfp4_gemv.so --------------------------------------------------------------------------------- */
 
