@@ -120,6 +120,9 @@ __global__ void __launch_bounds__(kStreamThreads, 1) moe_decode_stream_kernel(co
     __shared__ uint32_t s_want;                   // the generation this launch publishes and waits for
     __shared__ volatile int failed;
     __shared__ uint32_t red[32];
+    __shared__ __align__(16) uint32_t cand_key[64];   // router: the best k of each of 8 groups of 32 experts
+    __shared__ __align__(16) int cand_idx[64];
+    __shared__ float pick_score[8];
     // mailbox of the service warps, three slots used round robin by attempt: {arrivals, OR of flags, largest magnitude}
     __shared__ uint32_t svc_cnt[3], svc_flags[3], svc_amax[3];
     pdl_launch_dependents();
@@ -230,31 +233,55 @@ __global__ void __launch_bounds__(kStreamThreads, 1) moe_decode_stream_kernel(co
 
     // per-slot state of a streaming warp: the task in the slot (>= n_total: none) and its description
     int tk0 = n_total, tk1 = n_total, td0 = 0, td1 = 0;
+    // the first task is claimed before the expert table is known (that needs nothing from the router) ...
+    auto prologue_claim = [&]() {
+        tk0 = claim();
+        if (tk0 < n_total) td0 = describe(tk0);
+        tk1 = -1;                                              // free: requested when slot 0 has landed
+    };
+    // ... and requested as soon as it is
     auto prologue = [&]() {
+        if (tk0 < n_total) issue(tk0, td0, 0);
         if (warp == 0) {
             issue_ascale(0);
             if (a.E > 1) issue_ascale(1);
         }
-        tk0 = claim();
-        if (tk0 < n_total) { td0 = describe(tk0); issue(tk0, td0, 0); }
-        tk1 = -1;                                              // free: requested when slot 0 has landed
         if (warp == 1 || NW == 1) issue_bscale();
     };
 
     __syncthreads();                                           // barriers and the queue are initialised
     // stacked weights do not depend on the previous kernel in the stream: request them before waiting for it
+    if (!service) prologue_claim();
     if (!use_table && !service) prologue();
     pdl_wait();
-    if (warp == NW + NSV - 1 && lane == 0) s_want = ld_relaxed_gpu(sync_epoch) + 1u;   // (warp 0 is busy routing)
+    if (warp == NW + NSV - 1 && lane == 0) s_want = ld_relaxed_gpu(sync_epoch) + 1u;
+    // Router, spread over the CTA (the weight stream cannot start before the picks are known, so this is the
+    // critical path of the layer's start): warps 0..7 take 32 experts each, one per lane, and sort them; the best k
+    // of every warp are then ranked against one another (largest score, lowest expert index on ties - the
+    // reference's rule) and the k best of all enter the table.
+    constexpr int kRouteWarps = 8;
     if (routed) {
-        if (warp == 0) {
-            int id;
-            float w;
-            route_token<8>(rt.logits, rt.n_experts, rt.k, rt.score_func, rt.eps, rt.scaling, lane, id, w);
-            if (lane < rt.k) {
-                expert_of_slot[lane] = id;
-                weight_of_slot[lane] = w;
-                if (cta == 0) { rt.ids_out[lane] = id; rt.w_out[lane] = w; }
+        if (threadIdx.x < 8) { expert_of_slot[threadIdx.x] = 0; pick_score[threadIdx.x] = -INFINITY; }
+        if (warp < kRouteWarps) {
+            const int idx = warp * 32 + lane;
+            uint32_t key = 0u;
+            if (idx < rt.n_experts) key = route_key(route_score(__ldcg(rt.logits + idx), rt.score_func));
+            // the warp's 32 (key, lane) pairs sorted by a bitonic network, best first (on equal keys the lower lane):
+            // 15 compare-exchange steps, against k rounds of warp-wide arg-max with a reduction each
+            unsigned long long v = ((unsigned long long)key << 32) | (unsigned)(31 - lane);
+#pragma unroll
+            for (int k2 = 2; k2 <= 32; k2 <<= 1)
+#pragma unroll
+                for (int j = k2 >> 1; j > 0; j >>= 1) {
+                    const unsigned long long o = __shfl_xor_sync(kFullMask, v, j);
+                    const bool descending = (lane & k2) == 0;              // (k2 == 32: every lane)
+                    const bool keep_larger = ((lane & j) == 0) == descending;
+                    v = keep_larger ? (v > o ? v : o) : (v < o ? v : o);
+                }
+            if (lane < 8) {
+                const bool real = lane < rt.k && (uint32_t)(v >> 32) != 0u;
+                cand_key[warp * 8 + lane] = real ? (uint32_t)(v >> 32) : 0u;
+                cand_idx[warp * 8 + lane] = real ? warp * 32 + 31 - (int)(v & 31u) : 0x7fffffff;
             }
         }
     } else if (threadIdx.x < a.E) {
@@ -273,15 +300,49 @@ __global__ void __launch_bounds__(kStreamThreads, 1) moe_decode_stream_kernel(co
 #pragma unroll
         for (int off = 16; off > 0; off >>= 1) m = max(m, __shfl_xor_sync(kFullMask, m, off));
         if (lane == 0) red[warp] = m;
-        __syncthreads();                                       // also publishes the expert table and s_want
-        if (use_table && !service) prologue();
+        __syncthreads();                                       // candidates, s_want, the table of the unrouted entries
+        if (use_table && !routed && !service) prologue();
+        if (routed) {
+            // rank of a candidate among all 64 entries (empty ones carry key 0): how many are better.  Eight
+            // consecutive lanes share a candidate, each compares it with the eight entries of one group.
+            static_assert(kStreamThreads == 512, "64 candidates x 8 lanes");
+            const int c = threadIdx.x >> 3, part = threadIdx.x & 7;
+            const uint32_t ck = cand_key[c];
+            const int ci = cand_idx[c];
+            const uint4 k0 = *reinterpret_cast<const uint4*>(cand_key + part * 8);
+            const uint4 k1 = *reinterpret_cast<const uint4*>(cand_key + part * 8 + 4);
+            const int4 i0 = *reinterpret_cast<const int4*>(cand_idx + part * 8);
+            const int4 i1 = *reinterpret_cast<const int4*>(cand_idx + part * 8 + 4);
+            const uint32_t ok[8] = {k0.x, k0.y, k0.z, k0.w, k1.x, k1.y, k1.z, k1.w};
+            const int oi[8] = {i0.x, i0.y, i0.z, i0.w, i1.x, i1.y, i1.z, i1.w};
+            int rank = 0;
+#pragma unroll
+            for (int q = 0; q < 8; ++q) rank += (int)(ok[q] > ck) | ((int)(ok[q] == ck) & (int)(oi[q] < ci));
+            rank += __shfl_xor_sync(kFullMask, rank, 1);
+            rank += __shfl_xor_sync(kFullMask, rank, 2);
+            rank += __shfl_xor_sync(kFullMask, rank, 4);
+            if (part == 0 && ck != 0u && rank < rt.k) { expert_of_slot[rank] = ci; pick_score[rank] = route_key_score(ck); }
+        }
         m = 0;
 #pragma unroll
         for (int w = 0; w < NW + NSV; ++w) m = max(m, red[w]);
         float inv;
         xs = fp16_scale_for(m, inv);
         if (mine) store8_as_half(xvec, threadIdx.x, v, inv);
-        __syncthreads();
+        __syncthreads();                                       // the routed table, x in shared memory
+        if (routed && !service) prologue();
+        if (routed && warp == 0) {
+            // the picks' weights (needed only by the combine at the end); a pick that does not exist (fewer than k
+            // scores that are numbers) keeps expert 0 with weight 0 and is reported through the status word
+            const float sc = lane < rt.k ? pick_score[lane] : -INFINITY;
+            const float w = route_weight(sc, pick_score[0], rt.k, rt.score_func, rt.eps, rt.scaling, lane);
+            if (lane < rt.k) {
+                const bool missing = sc == -INFINITY;
+                weight_of_slot[lane] = missing ? 0.f : w;
+                if (missing) atomicExch(&g_device_status, 4);
+                if (cta == 0) { rt.ids_out[lane] = expert_of_slot[lane]; rt.w_out[lane] = missing ? 0.f : w; }
+            }
+        }
     }
     const uint32_t want = s_want;
     const uint32_t spin_limit = a.spin_limit;

@@ -22,6 +22,32 @@ struct RouteArgs {
     float* w_out;          // [n_tokens, k]
 };
 
+// Score of one expert from its logit (score_func 1; for softmax the logit itself orders and weighs).
+__device__ __forceinline__ float route_score(float g, int score_func) {
+    return score_func == 0 ? g : sqrtf(fmaxf(g, 0.0f) + log1pf(expf(-fabsf(g))));
+}
+
+// Order-preserving integer key of a score; 0 = never picked (NaN, -inf).
+__device__ __forceinline__ uint32_t route_key(float s) {
+    const uint32_t bits = __float_as_uint(s);
+    return (s != s || s == -INFINITY) ? 0u : (bits ^ ((bits >> 31) ? 0xffffffffu : 0x80000000u));
+}
+__device__ __forceinline__ float route_key_score(uint32_t key) {
+    return key != 0u ? __uint_as_float((key >> 31) ? (key ^ 0x80000000u) : ~key) : -INFINITY;
+}
+
+// Weight of pick `lane` (< k) from the picks' scores, by one warp: lane j holds pick j's score, `top` is the largest
+// score (pick 0's).  The same sum order wherever it is called, so that the fused and the stand-alone router agree
+// bit for bit.
+__device__ __forceinline__ float route_weight(float my_score, float top, int k, int score_func, float eps,
+                                              float scaling, int lane) {
+    const float mine = lane < k ? (score_func == 0 ? __expf(my_score - top) : my_score) : 0.f;
+    float sum = mine;
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) sum += __shfl_xor_sync(kFullMask, sum, off);
+    return score_func == 0 ? mine / sum : mine / (sum + eps) * scaling;
+}
+
 // PL: scores held per lane (experts <= 32 * PL).  On return lane j < k holds pick j in (id, w).
 template <int PL>
 __device__ __forceinline__ void route_token(const float* __restrict__ row, int n_experts, int k, int score_func,
@@ -40,20 +66,14 @@ __device__ __forceinline__ void route_token(const float* __restrict__ row, int n
     } else {
 #pragma unroll
         for (int i = 0; i < PL; ++i)
-            if (s[i] != -INFINITY) {
-                const float g = s[i];
-                s[i] = sqrtf(fmaxf(g, 0.0f) + log1pf(expf(-fabsf(g))));
-            }
+            if (s[i] != -INFINITY) s[i] = route_score(s[i], 1);
     }
     // Top-k by k rounds of warp-wide arg-max on order-preserving integer keys (redux.sync): largest score, lowest
     // expert index on ties; NaN scores are never picked.
     uint32_t key[PL];
 #pragma unroll
-    for (int i = 0; i < PL; ++i) {
-        const uint32_t bits = __float_as_uint(s[i]);
-        key[i] = (s[i] != s[i] || s[i] == -INFINITY) ? 0u : (bits ^ ((bits >> 31) ? 0xffffffffu : 0x80000000u));
-    }
-    float my_score = 0.f, sum = 0.f;
+    for (int i = 0; i < PL; ++i) key[i] = route_key(s[i]);
+    float my_score = 0.f;
     id = -1;
     // the lane's best key and where it sits: recomputed only by the lane that has just given a pick away
     uint32_t best = 0;
@@ -85,15 +105,7 @@ __device__ __forceinline__ void route_token(const float* __restrict__ row, int n
                 if (key[i] > best) { best = key[i]; best_i = i; }
         }
     }
-    // the weights need the picks only: one exponential per lane instead of one per round
-    {
-        const float mine = lane < k ? (score_func == 0 ? __expf(my_score - row_max) : my_score) : 0.f;
-        sum = mine;
-#pragma unroll
-        for (int off = 16; off > 0; off >>= 1) sum += __shfl_xor_sync(kFullMask, sum, off);
-        my_score = mine;
-    }
-    w = score_func == 0 ? my_score / sum : my_score / (sum + eps) * scaling;
+    w = route_weight(my_score, row_max, k, score_func, eps, scaling, lane);
 }
 
 }  // namespace dsv4
