@@ -311,9 +311,61 @@ def batched_configs(rt, qz, torch, dist, bank, dev, rank, world):
                       if equal else "all_to_all_single (NCCL): one row per (token, owner rank) out, partial rows back"),
                      "ms_all_gather_then_peer_combine_variant": ms_peer_combine,
                      "ms_gather_reduce_scatter_variant": ms_gathered, "ms_all_to_all_variant": ms_a2a}
+    if world == 1:
+        out["token_sweep_uniform_routing"] = batched_token_sweep(rt, torch, bank, dev)
     if rt.moe_device_status() != 0:
         raise RuntimeError("a batched kernel gave up on a bounded wait")
     return out
+
+
+def batched_token_sweep(rt, torch, bank, dev):
+    """The batched layer over 4096, 16384 and 65536 tokens (uniform top-6 routing over the resident bank), against
+    the bound that applies: the slower of (every expert's weights + the tokens once over HBM at the measured copy
+    bandwidth) and (the FP4 flops the path EXECUTES - three activation terms, 3 x the useful flops - at the FP4 peak
+    the library's own microbenchmark of tcgen05.mma kind::mxf4 gives on this device)."""
+    E = bank["w1p"].shape[0]
+    props = torch.cuda.get_device_properties(dev)
+    sm_hz = props.clock_rate * 1e3                       # maximum SM clock
+    clk_n256 = rt.mma_clocks(256, 0, device=dev)
+    clk_n192 = rt.mma_clocks(192, 0, device=dev)
+    clk_n192_copies = rt.mma_clocks(192, 4, device=dev)  # the GEMM kernels issue one scale-atom copy per MMA
+    fp4_peak = props.multi_processor_count * sm_hz * 2 * 128 * 256 * 64 / clk_n256 / 1e12
+    fp4_as_issued = props.multi_processor_count * sm_hz * 2 * 128 * 192 * 64 / clk_n192_copies / 1e12
+    hbm = measured_hbm_peak()[0]
+    res = {"fp4_microbenchmark": {"what": "tcgen05.mma kind::mxf4, M = 128, K = 64, one issuing thread per SM, 8000 MMAs",
+                                  "clocks_per_mma_n256": clk_n256, "clocks_per_mma_n192": clk_n192,
+                                  "clocks_per_mma_n192_with_one_scale_copy_per_mma": clk_n192_copies,
+                                  "sm_clock_mhz_assumed": sm_hz / 1e6, "fp4_peak_tflops": fp4_peak,
+                                  "fp4_tflops_at_the_kernels_tile_shape": fp4_as_issued}}
+    for T in (4096, 16384, 65536):
+        g = torch.Generator().manual_seed(4000 + T)
+        ids = torch.rand(T, E, generator=g).topk(TOP_K).indices.to(torch.int32).to(dev)
+        w = torch.softmax(torch.randn(T, TOP_K, generator=g), -1).float().to(dev)
+        x = torch.randn(T, HIDDEN, generator=g).to(torch.bfloat16).to(dev)
+        ws = torch.empty(rt.forward_workspace_bytes(T, TOP_K, HIDDEN, EXPERT_FF, HIDDEN, E), dtype=torch.uint8, device=dev)
+        y = torch.empty(T, HIDDEN, dtype=torch.bfloat16, device=dev)
+        for _ in range(2):
+            rt.moe_forward(bank, x, ids, w, out=y, workspace=ws)
+        torch.cuda.synchronize()
+        iters = 5 if T <= 16384 else 3
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(iters):
+            rt.moe_forward(bank, x, ids, w, out=y, workspace=ws)
+        b.record()
+        torch.cuda.synchronize()
+        ms = a.elapsed_time(b) / iters
+        flops = T * TOP_K * 2 * 3 * HIDDEN * EXPERT_FF
+        min_bytes = E * BYTES_PER_EXPERT + 2 * T * HIDDEN * 2
+        hbm_ms = min_bytes / hbm / 1e6
+        fp4_ms = 3 * flops / fp4_peak / 1e9
+        res[f"tokens_{T}"] = {"ms": ms, "tflops_useful": flops / ms / 1e9, "tflops_fp4_executed": 3 * flops / ms / 1e9,
+                              "frac_of_fp4_peak_executed": 3 * flops / ms / 1e9 / fp4_peak,
+                              "bound": "hbm" if hbm_ms > fp4_ms else "fp4 tensor", "bound_ms": max(hbm_ms, fp4_ms),
+                              "frac_of_bound": max(hbm_ms, fp4_ms) / ms}
+        del ws, x, y
+        torch.cuda.empty_cache()
+    return res
 
 
 def batched_small(rt, torch, bank, dev, T, steps, warmup):

@@ -268,6 +268,25 @@ inline bool dense_pdl_enabled() {
     return v == 1;
 }
 
+// CTAs per SM that one launch asks for.  Two fill the machine (126 registers x 256 threads) and are what a large
+// matrix wants.  A matrix small enough that one CTA per SM requests all of its rows up front (two batches of
+// kDenseRows per warp) is bound by the launch chain instead: with one CTA per SM the next launch of the chain
+// becomes resident beside this one and has its weights on the way while this one finishes (2048 x 4096 MXFP4:
+// 4.3 us per call against 5.6).  DSV4_B200_DENSE_WAVES = 1 .. 4 overrides the choice.
+inline int dense_waves(int n_rows, int n_blk) {
+    static int forced = -1;
+    if (forced < 0) {
+        const char* e = std::getenv("DSV4_B200_DENSE_WAVES");
+        const int w = e ? std::atoi(e) : 0;
+        forced = (w >= 1 && w <= 4) ? w : 0;
+    }
+    if (forced > 0) return forced;
+    const int n_slices = (n_blk + 31) >> 5;
+    const int n_groups = (kDenseThreads / 32) / n_slices > 0 ? (kDenseThreads / 32) / n_slices : 1;
+    const long long up_front = 2LL * kDenseRows * n_groups * dense_sm_count();
+    return n_rows <= up_front ? 1 : 2;
+}
+
 // Launches the aligned streaming kernel when it can, the byte-wise one otherwise.
 template <class Fmt, class Sc>
 inline cudaError_t dense_launch(const DenseArgs& a, cudaStream_t stream) {
@@ -277,7 +296,7 @@ inline cudaError_t dense_launch(const DenseArgs& a, cudaStream_t stream) {
         dense_gemv_unaligned_kernel<Fmt, Sc><<<(a.N + warps - 1) / warps, warps * 32, 0, stream>>>(a);
         return cudaGetLastError();
     }
-    long long grid = 2LL * dense_sm_count();
+    long long grid = (long long)dense_waves(a.N, a.K / Fmt::kElems) * dense_sm_count();
     const long long need = ((long long)a.N + kDenseCap - 1) / kDenseCap;
     if (grid < need) grid = need;
     if (grid > a.N) grid = a.N;

@@ -9,6 +9,7 @@
 // Nothing is allocated; all scratch lives in the caller's workspace.
 #include "moe_gemm_kernel.cuh"
 #include "moe_gemm_mxf4.cuh"
+#include "moe_mma_rate.cuh"
 
 #include <cstdio>
 #include <cstdlib>
@@ -396,4 +397,26 @@ DSV4_API int mxfp4_moe_forward_ep2(void* const* x_ptrs, void* const* ids_ptrs, v
     return moe_forward_impl(1, nullptr, bank_W1_packed, bank_W3_packed, bank_W2_packed, bank_W1_scale, bank_W3_scale,
                             bank_W2_scale, ids_local, w_local, n_tokens, n_experts_local, K_in, hidden, out_dim, k,
                             nullptr, workspace, stream, &peer, &in);
+}
+
+// Tensor-pipe clocks of one tcgen05.mma kind::mxf4 (M = 128, K = 64, N = n_cols: a multiple of 16 in 16 .. 256) with
+// `scale_copies` (0 .. 8) scale-atom copies issued in front of every four MMAs; one CTA per SM, `iters` rounds of
+// four MMAs.  clocks_per_mma: HOST pointer.  `scratch`: 8 bytes of device memory.  Synchronises the stream.
+// Returns 0, -1 bad argument, -3 launch / execution failure.
+DSV4_API int mxfp4_moe_mma_rate(int n_cols, int scale_copies, int iters, void* scratch, double* clocks_per_mma,
+                                cudaStream_t stream) {
+    if (n_cols < 16 || n_cols > 256 || n_cols % 16 != 0 || scale_copies < 0 || scale_copies > 8 || iters <= 0 ||
+        iters > (1 << 20) || !scratch || !clocks_per_mma)
+        return -1;
+    static int done[64] = {0};
+    if (allow_smem(mxf4_mma_rate_kernel, kRateBytes, done) != cudaSuccess) return -3;
+    long long* dev_clocks = reinterpret_cast<long long*>(scratch);
+    mxf4_mma_rate_kernel<<<sm_count(), 128, kRateBytes, stream>>>(n_cols, 8, scale_copies, dev_clocks);       // warm-up
+    mxf4_mma_rate_kernel<<<sm_count(), 128, kRateBytes, stream>>>(n_cols, iters, scale_copies, dev_clocks);
+    long long clocks = 0;
+    if (cudaMemcpyAsync(&clocks, dev_clocks, sizeof(clocks), cudaMemcpyDeviceToHost, stream) != cudaSuccess ||
+        cudaStreamSynchronize(stream) != cudaSuccess || cudaGetLastError() != cudaSuccess)
+        return -3;
+    *clocks_per_mma = (double)clocks / (4.0 * iters);
+    return 0;
 }

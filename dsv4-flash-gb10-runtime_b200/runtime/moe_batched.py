@@ -55,6 +55,20 @@ def moe_forward(bank: Dict[str, torch.Tensor], x: torch.Tensor, ids: torch.Tenso
     return out
 
 
+def mma_clocks(n_cols: int = 256, scale_copies: int = 0, iters: int = 2000, device=None) -> float:
+    """Tensor-pipe clocks of one `tcgen05.mma kind::mxf4` (M = 128, K = 64, N = n_cols) with `scale_copies` scale-atom
+    copies in front of every four MMAs: the library's own microbenchmark (one CTA per SM)."""
+    import ctypes
+    device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+    scratch = torch.zeros(1, dtype=torch.int64, device=device)
+    out = ctypes.c_double(0.0)
+    rc = _capi.load("moe").mxfp4_moe_mma_rate(c_int(n_cols), c_int(scale_copies), c_int(iters), _capi.ptr(scratch),
+                                              ctypes.cast(ctypes.byref(out), ctypes.c_void_p), _capi.stream_ptr(device))
+    if rc != 0:
+        raise RuntimeError(f"mxfp4_moe_mma_rate returned {rc}")
+    return float(out.value)
+
+
 def moe_device_status() -> int:
     """0 unless a kernel of the batched library gave up on a bounded wait or met a bad expert id (synchronises)."""
     return int(_capi.load("moe").mxfp4_moe_device_status())

@@ -196,6 +196,12 @@ size_t mxfp4_moe_forward_workspace_bytes(int n_tokens, int k, int K_in, int hidd
 /* 0, or the code a kernel of this library recorded since the last call (3 bad expert id, 4/5/6 a bounded wait ran
  * out); clears it.  Synchronises the device. */
 int mxfp4_moe_device_status(void);
+/* Microbenchmark of the instruction the batched layer is built on (no counterpart in the reference): tensor-pipe clocks
+ * of one tcgen05.mma kind::mxf4 (M = 128, K = 64, N = n_cols: a multiple of 16 in 16 .. 256) with `scale_copies`
+ * (0 .. 8) scale-atom copies in front of every four MMAs, one CTA per SM, `iters` rounds of four MMAs.  scratch: 8 bytes
+ * of device memory; clocks_per_mma: HOST pointer.  Synchronises the stream.  FP4 peak of the device =
+ * SMs x SM clock x 2 x 128 x n_cols x 64 / clocks.  Returns 0, -1 bad argument, -3 launch / execution failure. */
+int mxfp4_moe_mma_rate(int n_cols, int scale_copies, int iters, void* scratch, double* clocks_per_mma, void* stream);
 
 /* Expert parallel with the combine fused into the exchange: mxfp4_moe_forward over the gathered batch of
  * world * tokens_per_rank tokens (token t belongs to rank t / tokens_per_rank; ids index this rank's local bank, -1
