@@ -296,6 +296,26 @@ def batched_configs(rt, qz, torch, dist, bank, dev, rank, world):
         ms_a2a = timed_ms(step_a2a) if world > 1 and equal else None
         ms_gathered = timed_ms(step_gathered) if world > 1 and equal else None
         ms_peer_combine = timed_ms(step_peer_combine) if world > 1 and equal else None
+        # where one layer's time goes: one more call with events between its steps (slower than the timed calls: the
+        # events take away the overlap between consecutive kernels); with several ranks, the largest value per step
+        rt.stage_timing(True)
+        marks = []
+        if world > 1 and equal:
+            ep.ep_moe_forward_peer_inputs(peer_ctx, x_l, ids_l, w_l, E, local_bank, marks=marks)
+        else:
+            step()
+        torch.cuda.synchronize()
+        stage_us = dict(rt.stage_times())
+        rt.stage_timing(False)
+        for (_, before), (label, after) in zip(marks[:-1], marks[1:]):
+            stage_us["ep_" + label] = before.elapsed_time(after) * 1e3
+        if "ep_layer" in stage_us:     # the layer call holds the six kernel stages (and the id kernel in front of them)
+            stage_us["ep_layer_other"] = stage_us.pop("ep_layer") - sum(stage_us[n] for n in rt.STAGES)
+        if world > 1:
+            names = sorted(stage_us)
+            t = torch.tensor([stage_us[n] for n in names], device=dev, dtype=torch.float64)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            stage_us = dict(zip(names, (float(v) for v in t.tolist())))
         distinct = int(ids.unique().numel())
         flops = T * TOP_K * 2 * 3 * HIDDEN * EXPERT_FF
         min_bytes = distinct * BYTES_PER_EXPERT + 2 * T * HIDDEN * 2
@@ -304,6 +324,7 @@ def batched_configs(rt, qz, torch, dist, bank, dev, rank, world):
                      "frac_of_measured_hbm_peak": min_bytes / ms / 1e6 / world / measured_hbm_peak()[0],
                      "gbs_min_bytes": min_bytes / ms / 1e6, "distinct_experts": distinct,
                      "max_abs_vs_1gpu_over_inf_norm": parity,
+                     "stage_us_one_timed_call_max_over_ranks": stage_us,
                      "exchange": "none" if world == 1 else
                      ("peer memory over NVLink on both sides (symmetric memory, no collective library): tokens read by the "
                       "layer's kernels from the rank that published them, partial rows stored by its combine kernel "
@@ -837,8 +858,9 @@ def run_gpu(args, rank: int, world: int, local_rank: int):
                                  "max_abs_vs_1gpu_over_inf_norm": b["max_abs_vs_1gpu_over_inf_norm"],
                                  "ms_all_to_all_variant": b["ms_all_to_all_variant"],
                                  "ms_gather_reduce_scatter_variant": b["ms_gather_reduce_scatter_variant"],
-                                 "ms_all_gather_then_peer_combine_variant": b["ms_all_gather_then_peer_combine_variant"]}
-                          for name, b in batched.items()}
+                                 "ms_all_gather_then_peer_combine_variant": b["ms_all_gather_then_peer_combine_variant"],
+                                 "stage_us_one_timed_call_max_over_ranks": b["stage_us_one_timed_call_max_over_ranks"]}
+                          for name, b in batched.items() if name.startswith("config")}
     if dense is not None:
         line["dense"] = dense
     if world == 1:

@@ -104,7 +104,43 @@ cudaError_t launch_k(void (*kernel)(Params...), dim3 grid, dim3 block, size_t sm
     return cudaLaunchKernelEx(&cfg, kernel, std::forward<Args>(args)...);
 }
 
+// Stage timing (diagnostic; off by default): when switched on, the block-scaled path records an event before its
+// first kernel and after each of its kernels; mxfp4_moe_stage_times turns them into microseconds.  Events between
+// the launches take away the overlap of programmatic dependent launch, so a timed call is slower than a normal one.
+constexpr int kStageMarks = 7;      // start, group, quantise x, gate/up GEMM, quantise intermediate, down GEMM, combine
+bool g_stage_timing = false;
+cudaEvent_t g_stage_event[kStageMarks] = {};
+
+void stage_mark(cudaStream_t stream, int i) {
+    if (!g_stage_timing) return;
+    if (!g_stage_event[i] && cudaEventCreate(&g_stage_event[i]) != cudaSuccess) return;
+    cudaEventRecord(g_stage_event[i], stream);
+}
+
 }  // namespace
+
+// Switches the stage timing of the block-scaled batched path on (1) or off (0); returns the previous setting.
+// Not thread-safe; meant for one timed call on one stream at a time.
+DSV4_API int mxfp4_moe_stage_timing(int enable) {
+    const int before = g_stage_timing ? 1 : 0;
+    g_stage_timing = enable != 0;
+    return before;
+}
+
+// Microseconds of the six stages of the last timed call (group, quantise x, gate/up GEMM, quantise intermediate,
+// down GEMM, combine) into us_out[0..6); synchronises on the last event.  Returns 0, -1 if no timed call was made.
+DSV4_API int mxfp4_moe_stage_times(float* us_out) {
+    if (!us_out) return -1;
+    for (int i = 0; i < kStageMarks; ++i)
+        if (!g_stage_event[i]) return -1;
+    if (cudaEventSynchronize(g_stage_event[kStageMarks - 1]) != cudaSuccess) return -1;
+    for (int i = 0; i + 1 < kStageMarks; ++i) {
+        float ms = 0.f;
+        if (cudaEventElapsedTime(&ms, g_stage_event[i], g_stage_event[i + 1]) != cudaSuccess) return -1;
+        us_out[i] = ms * 1e3f;
+    }
+    return 0;
+}
 
 // Bytes of workspace mxfp4_moe_forward needs (normalised activations, grouping tables, the fp16 intermediate
 // [n_tokens * k, hidden] and the FP32 per-pair outputs [n_tokens * k, out_dim]).
@@ -158,12 +194,14 @@ static int moe_forward_impl(int path, const __nv_bfloat16* x, const uint8_t* ban
 
     int* status = nullptr;
     cudaGetSymbolAddress(reinterpret_cast<void**>(&status), g_device_status);
+    stage_mark(stream, 0);
     if (path == 1)
         launch_k(moe_group_kernel, dim3(1), dim3(1024), 0, stream, ids, P, n_experts, hidden / kMoeTileRows,
                  (out_dim + kQRowsDown - 1) / kQRowsDown, kQTokUp, kQTokDown, g, status);
     else
         launch_k(moe_group_kernel, dim3(1), dim3(1024), 0, stream, ids, P, n_experts, hidden / kMoeTileRows,
                  out_dim / kMoeTileRows, kMoeTileTokens, kMoeTileTokens, g, status);
+    stage_mark(stream, 1);
     const int grid = sm_count();
 
     if (path == 1) {
@@ -173,12 +211,15 @@ static int moe_forward_impl(int path, const __nv_bfloat16* x, const uint8_t* ban
         uint8_t* mq = ws + m.mq; uint8_t* ms = ws + m.ms;
         float* midf = reinterpret_cast<float*>(ws + m.midf);
         const int qgrid = 4 * grid;
+        // a token none of whose experts is in this bank (expert parallel: they all live on other ranks) is not read
+        const int* no_rows = nullptr;
         if (peer_in)
             launch_k(moe_quantize_mxfp4x3_kernel<__nv_bfloat16, true>, dim3(qgrid), dim3(256), 0, stream, x,
-                     (long long)n_tokens, K_in, xq, xs, *peer_in);
+                     (long long)n_tokens, K_in, xq, xs, *peer_in, no_rows, ids, k);
         else
             launch_k(moe_quantize_mxfp4x3_kernel<__nv_bfloat16, false>, dim3(qgrid), dim3(256), 0, stream, x,
-                     (long long)n_tokens, K_in, xq, xs, MoePeerIn{});
+                     (long long)n_tokens, K_in, xq, xs, MoePeerIn{}, no_rows, ids, k);
+        stage_mark(stream, 2);
         MoeQGemmArgs qu;
         qu.wa_p = bank_W1_packed; qu.wb_p = bank_W3_packed; qu.wa_s = bank_W1_scale; qu.wb_s = bank_W3_scale;
         qu.stride_p = (long long)hidden * (K_in / 2); qu.stride_s = (long long)hidden * (K_in / 32);
@@ -187,8 +228,13 @@ static int moe_forward_impl(int path, const __nv_bfloat16* x, const uint8_t* ban
         cudaError_t qerr = allow_smem(moe_gemm_mxf4_kernel<0>, MoeQGemmLayout<0>::kBytes, qup_done);
         if (qerr == cudaSuccess) {
             launch_k(moe_gemm_mxf4_kernel<0>, dim3(grid), dim3(kGemmThreads), MoeQGemmLayout<0>::kBytes, stream, qu);
+            stage_mark(stream, 3);
+            // only the rows that exist: the pairs of this bank's experts fill slots [0, offsets[n_experts])
+            const int* used = g.offsets + n_experts;
+            const int* no_ids = nullptr;
             launch_k(moe_quantize_mxfp4x3_kernel<float, false>, dim3(qgrid), dim3(256), 0, stream, midf, (long long)P,
-                     hidden, mq, ms, MoePeerIn{});
+                     hidden, mq, ms, MoePeerIn{}, used, no_ids, 0);
+            stage_mark(stream, 4);
             qerr = cudaGetLastError();
         }
         MoeQGemmArgs qd = qu;
@@ -198,11 +244,13 @@ static int moe_forward_impl(int path, const __nv_bfloat16* x, const uint8_t* ban
         if (qerr == cudaSuccess) qerr = allow_smem(moe_gemm_mxf4_kernel<1>, MoeQGemmLayout<1>::kBytes, qdown_done);
         if (qerr == cudaSuccess) {
             launch_k(moe_gemm_mxf4_kernel<1>, dim3(grid), dim3(kGemmThreads), MoeQGemmLayout<1>::kBytes, stream, qd);
-            dim3 cgrid((out_dim / 4 + 127) / 128, n_tokens);
+            stage_mark(stream, 5);
+            dim3 cgrid((out_dim / 4 + 127) / 128, n_tokens < 65535 ? n_tokens : 65535);
             if (peer)
                 launch_k(moe_combine_peer_kernel, dim3(cgrid), dim3(128), 0, stream, y, g.pair_slot, n_tokens, k, out_dim, *peer);
             else
                 launch_k(moe_combine_kernel, dim3(cgrid), dim3(128), 0, stream, y, g.pair_slot, n_tokens, k, out_dim, out);
+            stage_mark(stream, 6);
             qerr = cudaGetLastError();
         }
         if (qerr != cudaSuccess) {
@@ -236,7 +284,7 @@ static int moe_forward_impl(int path, const __nv_bfloat16* x, const uint8_t* ban
         err = cudaGetLastError();
     }
     if (err == cudaSuccess) {
-        dim3 cgrid((out_dim / 4 + 127) / 128, n_tokens);
+        dim3 cgrid((out_dim / 4 + 127) / 128, n_tokens < 65535 ? n_tokens : 65535);
         if (peer)
             launch_k(moe_combine_peer_kernel, dim3(cgrid), dim3(128), 0, stream, y, g.pair_slot, n_tokens, k, out_dim, *peer);
         else

@@ -154,21 +154,22 @@ __global__ void moe_combine_kernel(const float* __restrict__ y, const int* __res
                                    int k, int O, __nv_bfloat16* __restrict__ out) {
     pdl_launch_dependents();
     pdl_wait();
-    const int t = blockIdx.y;
     const int o = (blockIdx.x * blockDim.x + threadIdx.x) * 4;
-    if (t >= n_tokens || o >= O) return;
-    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-    for (int j = 0; j < k; ++j) {
-        const int slot = pair_slot[t * k + j];
-        if (slot < 0) continue;
-        const float4 v = __ldcs(reinterpret_cast<const float4*>(y + (size_t)slot * O + o));
-        acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+    if (o >= O) return;
+    for (int t = blockIdx.y; t < n_tokens; t += gridDim.y) {         // grid.y is capped at 65 535
+        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+        for (int j = 0; j < k; ++j) {
+            const int slot = pair_slot[t * k + j];
+            if (slot < 0) continue;
+            const float4 v = __ldcs(reinterpret_cast<const float4*>(y + (size_t)slot * O + o));
+            acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+        }
+        __nv_bfloat162 lo = __floats2bfloat162_rn(acc.x, acc.y), hi = __floats2bfloat162_rn(acc.z, acc.w);
+        uint2 packed;
+        packed.x = *reinterpret_cast<uint32_t*>(&lo);
+        packed.y = *reinterpret_cast<uint32_t*>(&hi);
+        *reinterpret_cast<uint2*>(out + (size_t)t * O + o) = packed;
     }
-    __nv_bfloat162 lo = __floats2bfloat162_rn(acc.x, acc.y), hi = __floats2bfloat162_rn(acc.z, acc.w);
-    uint2 packed;
-    packed.x = *reinterpret_cast<uint32_t*>(&lo);
-    packed.y = *reinterpret_cast<uint32_t*>(&hi);
-    *reinterpret_cast<uint2*>(out + (size_t)t * O + o) = packed;
 }
 
 // Expert parallel: where the per-token sums of a rank go.  Token t of the gathered batch belongs to rank
@@ -210,26 +211,27 @@ __global__ void moe_combine_peer_kernel(const float* __restrict__ y, const int* 
                                         int k, int O, const MoePeerOut peer) {
     pdl_launch_dependents();
     pdl_wait();
-    const int t = blockIdx.y;
     const int o = (blockIdx.x * blockDim.x + threadIdx.x) * 4;
-    if (t >= n_tokens || o >= O) return;
-    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-    bool any = false;
-    for (int j = 0; j < k; ++j) {
-        const int slot = pair_slot[t * k + j];
-        if (slot < 0) continue;
-        any = true;
-        const float4 v = __ldcs(reinterpret_cast<const float4*>(y + (size_t)slot * O + o));
-        acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+    if (o >= O) return;
+    for (int t = blockIdx.y; t < n_tokens; t += gridDim.y) {         // grid.y is capped at 65 535
+        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+        bool any = false;
+        for (int j = 0; j < k; ++j) {
+            const int slot = pair_slot[t * k + j];
+            if (slot < 0) continue;
+            any = true;
+            const float4 v = __ldcs(reinterpret_cast<const float4*>(y + (size_t)slot * O + o));
+            acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+        }
+        if (!any) continue;                 // none of the token's experts lives here: the home rank skips this slice
+        __nv_bfloat162 lo = __floats2bfloat162_rn(acc.x, acc.y), hi = __floats2bfloat162_rn(acc.z, acc.w);
+        uint2 packed;
+        packed.x = *reinterpret_cast<uint32_t*>(&lo);
+        packed.y = *reinterpret_cast<uint32_t*>(&hi);
+        const int home = t / peer.tokens_per_rank, tl = t - home * peer.tokens_per_rank;
+        __nv_bfloat16* dst = peer.recv[home] + ((size_t)peer.my_rank * peer.tokens_per_rank + tl) * O + o;
+        *reinterpret_cast<uint2*>(dst) = packed;
     }
-    if (!any) return;                       // none of the token's experts lives here: the home rank skips this slice
-    __nv_bfloat162 lo = __floats2bfloat162_rn(acc.x, acc.y), hi = __floats2bfloat162_rn(acc.z, acc.w);
-    uint2 packed;
-    packed.x = *reinterpret_cast<uint32_t*>(&lo);
-    packed.y = *reinterpret_cast<uint32_t*>(&hi);
-    const int home = t / peer.tokens_per_rank, tl = t - home * peer.tokens_per_rank;
-    __nv_bfloat16* dst = peer.recv[home] + ((size_t)peer.my_rank * peer.tokens_per_rank + tl) * O + o;
-    *reinterpret_cast<uint2*>(dst) = packed;
 }
 
 // out[t, :] = bf16( sum_r recv[r][t, :] ), ranks in ascending order (fixed summation order), over the ranks that
@@ -273,17 +275,29 @@ __global__ void moe_ep_sum_kernel(const __nv_bfloat16* __restrict__ recv, const 
 // (K must be a multiple of 256): 16- or 32-byte loads, one 4-byte store per lane and term.
 // With PEER the rows are not in `src` but in the per-rank buffers of `in` (row t = row t % tokens_per_rank of rank
 // t / tokens_per_rank).
+// rows_used (device, may be null): only rows [0, *rows_used) are converted (the intermediate of an expert-parallel
+// rank holds rows for its own pairs only).  row_ids / k (may be null): row t is converted only if one of
+// row_ids[t * k .. t * k + k) is >= 0 (a token none of whose experts lives on this rank is never read).
 template <class Elem, bool PEER = false>
 __global__ void moe_quantize_mxfp4x3_kernel(const Elem* __restrict__ src, long long rows, int K,
-                                            uint8_t* __restrict__ q, uint8_t* __restrict__ s, const MoePeerIn in = {}) {
+                                            uint8_t* __restrict__ q, uint8_t* __restrict__ s, const MoePeerIn in = {},
+                                            const int* __restrict__ rows_used = nullptr,
+                                            const int* __restrict__ row_ids = nullptr, int k = 0) {
     pdl_launch_dependents();
     pdl_wait();
     const int lane = threadIdx.x & 31;
-    const long long n_chunks = rows * (K / 256);
+    const long long live_rows = rows_used ? min(rows, (long long)__ldg(rows_used)) : rows;
+    const long long n_chunks = live_rows * (K / 256);
     const long long term_q = rows * (K / 2), term_s = rows * (K / 32);
     for (long long w = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); w < n_chunks;
          w += (long long)gridDim.x * (blockDim.x >> 5)) {
         const long long e0 = w * 256 + 8 * lane;                    // first of this lane's eight elements (row-major)
+        if (row_ids) {
+            const long long row = e0 / K;
+            bool wanted = false;
+            for (int j = 0; j < k; ++j) wanted |= __ldg(row_ids + row * k + j) >= 0;
+            if (!wanted) continue;                                   // warp-uniform: a warp works on one row
+        }
         float v[8];
         if constexpr (sizeof(Elem) == 2) {
             const Elem* from = src + e0;

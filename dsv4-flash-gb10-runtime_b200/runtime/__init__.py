@@ -5,5 +5,5 @@ from .fp8_e4m3_gemv_binding import (fp8_e4m3_gemv, fp8_e4m3_gemv_batched, fp8_e4
 from .mxfp4_grouped_gemv_binding import (                                    # noqa: F401
     mxfp4_grouped_gemv, mxfp4_grouped_gemv_static, mxfp4_grouped_gemv_ids, mxfp4_dequant_bf16, moe_route_topk, device_status,
     moe_decode_layer, decode_workspace_bytes, decode_picks)
-from .moe_batched import moe_forward, forward_workspace_bytes, moe_device_status, mma_clocks   # noqa: F401
+from .moe_batched import moe_forward, forward_workspace_bytes, moe_device_status, mma_clocks, stage_timing, stage_times, STAGES   # noqa: F401
 from .bank_loader import load_expert_bank, load_shared_expert_fp8, SnapshotReader   # noqa: F401

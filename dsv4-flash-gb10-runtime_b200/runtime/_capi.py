@@ -38,6 +38,8 @@ SIGNATURES = {
         "mxfp4_moe_forward_ep2": (c_int, [_P] * 9 + [c_int] * 6 + [_P] + [c_int] * 2 + [_P, _P]),
         "mxfp4_moe_device_status": (c_int, []),
         "mxfp4_moe_mma_rate": (c_int, [c_int, c_int, c_int, _P, _P, _P]),
+        "mxfp4_moe_stage_timing": (c_int, [c_int]),
+        "mxfp4_moe_stage_times": (c_int, [_P]),
     },
     "fp8": {
         "fp8_e4m3_gemv_m1": (c_int, [_P, _P, _P, c_int, c_int, c_int64, c_int64, _P, _P]),

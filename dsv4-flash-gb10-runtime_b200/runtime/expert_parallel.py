@@ -246,13 +246,22 @@ def ep_moe_forward_peer(ctx: PeerCombine, x: torch.Tensor, ids: torch.Tensor, we
 
 
 def ep_moe_forward_peer_inputs(ctx: PeerCombine, x: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor,
-                               n_experts: int, local_bank: Dict[str, torch.Tensor]) -> torch.Tensor:
+                               n_experts: int, local_bank: Dict[str, torch.Tensor],
+                               marks: Optional[list] = None) -> torch.Tensor:
     """ep_moe_forward_peer without any collective library on the path: every rank copies its tokens (activations,
     ids, weights) into its published symmetric-memory buffers; after a barrier every rank runs its experts over the
     whole batch, READING each token from the rank that published it (the quantiser and a small id kernel load over
     NVLink) and storing each partial row into the home rank's receive buffer; a second barrier, then the rank-order
-    sum.  The context must have been built with in_dim and k.  Block-scaled tensor-core path only."""
+    sum.  The context must have been built with in_dim and k.  Block-scaled tensor-core path only.
+    `marks`: a list that receives (name, CUDA event) pairs after every step of the call (diagnostic timing)."""
     from ctypes import c_int
+
+    def mark(name):
+        if marks is not None:
+            ev = torch.cuda.Event(enable_timing=True)
+            ev.record()
+            marks.append((name, ev))
+
     from . import _capi
     lib = _capi.load("moe")
     world, rank = ctx.world, ctx.rank
@@ -264,10 +273,13 @@ def ep_moe_forward_peer_inputs(ctx: PeerCombine, x: torch.Tensor, ids: torch.Ten
     E_local, hidden, out_dim = local_bank["w1p"].shape[0], local_bank["w1p"].shape[1], local_bank["w2p"].shape[1]
     if out_dim != ctx.O or E_local != per:
         raise ValueError("ep_moe_forward_peer_inputs: bank does not match the context")
+    mark("start")
     ctx.pub_x.copy_(x)
     ctx.pub_ids.copy_(ids)
     ctx.pub_w.copy_(weights)
+    mark("publish")
     ctx.handle.barrier()                                             # every rank's tokens are published
+    mark("barrier_published")
     ws = torch.empty(lib.mxfp4_moe_forward_ep2_workspace_bytes(c_int(world), c_int(T), c_int(k), c_int(K), c_int(hidden),
                                                                c_int(out_dim), c_int(E_local)),
                      dtype=torch.uint8, device=x.device)
@@ -279,13 +291,16 @@ def ep_moe_forward_peer_inputs(ctx: PeerCombine, x: torch.Tensor, ids: torch.Ten
                                    c_int(rank), _capi.ptr(ws), _capi.stream_ptr(x.device))
     if rc != 0:
         raise RuntimeError(f"mxfp4_moe_forward_ep2 returned {rc}")
+    mark("layer")
     ctx.handle.barrier()                                             # every rank's partial rows have landed
+    mark("barrier_rows_landed")
     out = torch.empty(T, out_dim, dtype=torch.bfloat16, device=x.device)
     mine = ctx.buf[half * ctx.slab:(half + 1) * ctx.slab]
     rc = lib.mxfp4_moe_ep_sum(_capi.ptr(mine), _capi.ptr(ctx.pub_ids), c_int(k), c_int(per), c_int(world), c_int(T),
                               c_int(out_dim), _capi.ptr(out), _capi.stream_ptr(x.device))
     if rc != 0:
         raise RuntimeError(f"mxfp4_moe_ep_sum returned {rc}")
+    mark("sum")
     return out
 
 

@@ -69,6 +69,25 @@ def mma_clocks(n_cols: int = 256, scale_copies: int = 0, iters: int = 2000, devi
     return float(out.value)
 
 
+STAGES = ("group", "quantise_x", "gemm_gate_up", "quantise_intermediate", "gemm_down", "combine")
+
+
+def stage_timing(enable: bool) -> bool:
+    """Switch the stage timing of the block-scaled batched path on or off (diagnostic: a timed call loses the overlap
+    of programmatic dependent launch); returns the previous setting."""
+    return bool(_capi.load("moe").mxfp4_moe_stage_timing(c_int(1 if enable else 0)))
+
+
+def stage_times() -> Dict[str, float]:
+    """Microseconds per stage of the last call made while stage timing was on (synchronises on its last event)."""
+    import ctypes
+    buf = (ctypes.c_float * len(STAGES))()
+    rc = _capi.load("moe").mxfp4_moe_stage_times(ctypes.cast(buf, ctypes.c_void_p))
+    if rc != 0:
+        raise RuntimeError("no timed call of the batched layer to report")
+    return {name: float(buf[i]) for i, name in enumerate(STAGES)}
+
+
 def moe_device_status() -> int:
     """0 unless a kernel of the batched library gave up on a bounded wait or met a bad expert id (synchronises)."""
     return int(_capi.load("moe").mxfp4_moe_device_status())

@@ -202,6 +202,14 @@ int mxfp4_moe_device_status(void);
  * of device memory; clocks_per_mma: HOST pointer.  Synchronises the stream.  FP4 peak of the device =
  * SMs x SM clock x 2 x 128 x n_cols x 64 / clocks.  Returns 0, -1 bad argument, -3 launch / execution failure. */
 int mxfp4_moe_mma_rate(int n_cols, int scale_copies, int iters, void* scratch, double* clocks_per_mma, void* stream);
+/* Stage timing of the block-scaled batched path (diagnostic, off by default, not thread-safe; no counterpart in the
+ * reference).  mxfp4_moe_stage_timing(1) makes every later call record an event before its first kernel and after each
+ * of its kernels (a timed call loses the overlap of programmatic dependent launch); it returns the previous setting.
+ * mxfp4_moe_stage_times writes the microseconds of the last timed call's six stages - group, quantise x, gate/up GEMM,
+ * quantise intermediate, down GEMM, combine - to us_out[0..6) (HOST pointer) after synchronising on the last event;
+ * returns 0, or -1 when no timed call was made. */
+int mxfp4_moe_stage_timing(int enable);
+int mxfp4_moe_stage_times(float* us_out);
 
 /* Expert parallel with the combine fused into the exchange: mxfp4_moe_forward over the gathered batch of
  * world * tokens_per_rank tokens (token t belongs to rank t / tokens_per_rank; ids index this rank's local bank, -1
