@@ -296,6 +296,13 @@ def batched_configs(rt, qz, torch, dist, bank, dev, rank, world):
         ms_a2a = timed_ms(step_a2a) if world > 1 and equal else None
         ms_gathered = timed_ms(step_gathered) if world > 1 and equal else None
         ms_peer_combine = timed_ms(step_peer_combine) if world > 1 and equal else None
+        ms_published = None
+        if world > 1 and equal:      # the producer of the tokens wrote them where the peers read them: nothing to copy
+            peer_ctx.pub_x.copy_(x_l)
+            peer_ctx.pub_ids.copy_(ids_l)
+            peer_ctx.pub_w.copy_(w_l)
+            ms_published = timed_ms(lambda: ep.ep_moe_forward_peer_inputs(peer_ctx, peer_ctx.pub_x, peer_ctx.pub_ids,
+                                                                          peer_ctx.pub_w, E, local_bank))
         # where one layer's time goes: one more call with events between its steps (slower than the timed calls: the
         # events take away the overlap between consecutive kernels); with several ranks, the largest value per step
         rt.stage_timing(True)
@@ -331,6 +338,7 @@ def batched_configs(rt, qz, torch, dist, bank, dev, rank, world):
                       "into the home rank's buffer, two barriers, rank-order sum; no host synchronisation"
                       if equal else "all_to_all_single (NCCL): one row per (token, owner rank) out, partial rows back"),
                      "ms_all_gather_then_peer_combine_variant": ms_peer_combine,
+                     "ms_inputs_already_in_published_buffers": ms_published,
                      "ms_gather_reduce_scatter_variant": ms_gathered, "ms_all_to_all_variant": ms_a2a}
     if world == 1:
         out["token_sweep_uniform_routing"] = batched_token_sweep(rt, torch, bank, dev)
@@ -859,6 +867,7 @@ def run_gpu(args, rank: int, world: int, local_rank: int):
                                  "ms_all_to_all_variant": b["ms_all_to_all_variant"],
                                  "ms_gather_reduce_scatter_variant": b["ms_gather_reduce_scatter_variant"],
                                  "ms_all_gather_then_peer_combine_variant": b["ms_all_gather_then_peer_combine_variant"],
+                                 "ms_inputs_already_in_published_buffers": b["ms_inputs_already_in_published_buffers"],
                                  "stage_us_one_timed_call_max_over_ranks": b["stage_us_one_timed_call_max_over_ranks"]}
                           for name, b in batched.items() if name.startswith("config")}
     if dense is not None:

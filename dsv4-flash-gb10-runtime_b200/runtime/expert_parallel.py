@@ -274,15 +274,21 @@ def ep_moe_forward_peer_inputs(ctx: PeerCombine, x: torch.Tensor, ids: torch.Ten
     if out_dim != ctx.O or E_local != per:
         raise ValueError("ep_moe_forward_peer_inputs: bank does not match the context")
     mark("start")
-    ctx.pub_x.copy_(x)
-    ctx.pub_ids.copy_(ids)
-    ctx.pub_w.copy_(weights)
+    # a caller whose producer wrote straight into the published buffers (ctx.pub_x / pub_ids / pub_w) has nothing to copy
+    if x.data_ptr() != ctx.pub_x.data_ptr():
+        ctx.pub_x.copy_(x)
+    if ids.data_ptr() != ctx.pub_ids.data_ptr():
+        ctx.pub_ids.copy_(ids)
+    if weights.data_ptr() != ctx.pub_w.data_ptr():
+        ctx.pub_w.copy_(weights)
     mark("publish")
     ctx.handle.barrier()                                             # every rank's tokens are published
     mark("barrier_published")
-    ws = torch.empty(lib.mxfp4_moe_forward_ep2_workspace_bytes(c_int(world), c_int(T), c_int(k), c_int(K), c_int(hidden),
-                                                               c_int(out_dim), c_int(E_local)),
-                     dtype=torch.uint8, device=x.device)
+    need = int(lib.mxfp4_moe_forward_ep2_workspace_bytes(c_int(world), c_int(T), c_int(k), c_int(K), c_int(hidden),
+                                                         c_int(out_dim), c_int(E_local)))
+    ws = getattr(ctx, "_layer_ws", None)
+    if ws is None or ws.numel() < need:
+        ws = ctx._layer_ws = torch.empty(need, dtype=torch.uint8, device=x.device)
     half = ctx.next_half()
     rc = lib.mxfp4_moe_forward_ep2(ctx._x_ptrs, ctx._ids_ptrs, ctx._w_ptrs, _capi.ptr(local_bank["w1p"]),
                                    _capi.ptr(local_bank["w3p"]), _capi.ptr(local_bank["w2p"]), _capi.ptr(local_bank["w1s"]),

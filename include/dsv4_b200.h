@@ -103,7 +103,9 @@ int mxfp4_dequant_bf16(const uint8_t* packed, const uint8_t* scale, long long ro
                        void* stream);
 
 /* Added (diagnostic, no counterpart): 0 unless a kernel of this library gave up on one of its bounded waits since
- * the last call (1 = a gate/up row never landed, 2 = a down row, 3 = an expert's intermediate never became complete);
+ * the last call (1 = a gate/up row never landed, 2 = a down row, 3 = an expert's intermediate never became complete),
+ * or the router of mxfp4_moe_decode_layer found fewer than k pickable experts (4: NaN or -inf logits; the missing
+ * picks run with weight 0, where the reference's host router aborts with -2, routed.cu:186-199);
  * clears the status.  A kernel that gives up writes NaN to its output rows, so the damage is also visible downstream.
  * Synchronises the device. */
 int dsv4_b200_device_status(void);
