@@ -170,3 +170,51 @@ def test_configs_3_and_4_at_stated_size_against_the_oracle(rt, full_bank, name, 
     got = out[sample.to(dev)].float().cpu().numpy()
     err, cos = oracle.max_abs_rel(got, ref), oracle.cosine(got, ref)
     assert err <= 1e-2 and cos >= 0.9999, f"{name}: max-abs/inf {err:.3e} cosine {cos:.7f}"
+
+
+def test_moe_forward_65536_tokens_small_dims(rt, qz):
+    """More tokens than a grid dimension holds (the combine kernel walks tokens with a stride): 65 536 tokens at
+    small dimensions, a sample of tokens against the oracle."""
+    dev = torch.device("cuda:0")
+    T, E, K, H, O, k = 65536, 4, 256, 256, 128, 1
+    bank = qz.make_expert_bank(E, K, H, "cpu", seed=41)
+    g = torch.Generator().manual_seed(42)
+    w2 = (torch.randn(E, O, H, generator=g) * 0.02).to(torch.bfloat16)
+    bank["w2p"], bank["w2s"] = qz.quantize_mxfp4(w2)
+    x = torch.randn(T, K, generator=g).to(torch.bfloat16)
+    ids, w = routing(T, E, k, seed=43)
+    out = rt.moe_forward({n: v.to(dev) for n, v in bank.items()}, x.to(dev), ids.to(dev), w.to(dev))
+    torch.cuda.synchronize()
+    assert rt.moe_device_status() == 0
+    sample = torch.cat([torch.arange(0, 8), torch.arange(65528, 65536), torch.randint(0, T, (48,), generator=g)])
+    ref = oracle.moe_layer_ref(x[sample], bank, ids[sample].numpy(), w[sample].numpy())
+    got = out[sample.to(dev)].float().cpu().numpy()
+    err, cos = oracle.max_abs_rel(got, ref), oracle.cosine(got, ref)
+    assert err <= 1e-2 and cos >= 0.9999, f"max-abs/inf {err:.3e} cosine {cos:.7f}"
+
+
+def test_stage_timing_reports_six_stages_and_changes_nothing(rt, qz):
+    dev = torch.device("cuda:0")
+    T, E, K, H, k = 96, 8, 512, 512, 2
+    bank = {n: v.to(dev) for n, v in qz.make_expert_bank(E, K, H, "cpu", seed=51).items()}
+    x = torch.randn(T, K, generator=torch.Generator().manual_seed(52)).to(torch.bfloat16).to(dev)
+    ids, w = routing(T, E, k, seed=53)
+    plain = rt.moe_forward(bank, x, ids.to(dev), w.to(dev), path="mxf4")
+    assert rt.stage_timing(True) is False
+    try:
+        timed = rt.moe_forward(bank, x, ids.to(dev), w.to(dev), path="mxf4")
+        stages = rt.stage_times()
+    finally:
+        assert rt.stage_timing(False) is True
+    assert list(stages) == list(rt.STAGES) and all(0.0 < v < 1e5 for v in stages.values()), stages
+    assert torch.equal(plain.view(torch.int16), timed.view(torch.int16))
+
+
+def test_mma_rate_probe(rt):
+    """The library's tensor-pipe microbenchmark: a kind::mxf4 MMA of N = 256 takes longer than one of N = 64, scale
+    copies add to it, and the numbers are of the order the hardware allows (tens to a few hundred clocks)."""
+    n64, n256, n256_copies = rt.mma_clocks(64, 0, 500), rt.mma_clocks(256, 0, 500), rt.mma_clocks(256, 4, 500)
+    assert 30.0 < n64 <= n256 * 1.05 and n256 < 400.0, (n64, n256)
+    assert n256 < n256_copies < 1000.0, (n256, n256_copies)
+    with pytest.raises(RuntimeError):
+        rt.mma_clocks(250, 0, 10)                # N must be a multiple of 16
