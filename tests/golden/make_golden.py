@@ -20,7 +20,7 @@ import types
 import numpy as np
 import torch
 
-REF = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+REF = sys.argv[1] if len(sys.argv) > 1 else os.environ.get("DSV4_REFERENCE_ROOT", "/root/reference")
 sys.path.insert(0, os.path.join(REF, "runtime"))
 
 import e8m0_decode as ref_e8m0            # noqa: E402
