@@ -108,3 +108,19 @@ def test_adversarial_activations_dsv4_shape(rt, dev, small_bank, name, mode):
         gb.set_launch_mode(before)
     check(out, ref)
     assert rt.device_status() == 0
+
+
+def test_output_stored_straight_into_pinned_host_memory(rt, dev, small_bank):
+    """`out` may be pinned host memory (mapped on the device): the kernel's own stores are the device-to-host
+    transfer.  Bitwise equal to the output written to device memory."""
+    bank = {k: v.to(dev) for k, v in small_bank.items()}
+    g = torch.Generator().manual_seed(77)
+    x = torch.randn(K, generator=g).to(torch.bfloat16).to(dev)
+    logits = torch.randn(8, generator=g).to(dev)
+    ws = torch.empty(rt.decode_workspace_bytes(6, H, K), dtype=torch.uint8, device=dev)
+    on_device = rt.moe_decode_layer(bank, logits, x, k=6, score_func="softmax", workspace=ws).clone()
+    host = torch.full((K,), float("nan"), dtype=torch.bfloat16).pin_memory()
+    rt.moe_decode_layer(bank, logits, x, k=6, score_func="softmax", out=host, workspace=ws)
+    torch.cuda.synchronize()
+    assert torch.equal(host.view(torch.int16), on_device.cpu().view(torch.int16))
+    assert rt.device_status() == 0
