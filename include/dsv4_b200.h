@@ -90,7 +90,8 @@ int mxfp4_moe_route_topk(const float* logits, int n_tokens, int n_experts, int k
  * + routed-expert FFN over a resident bank.  logits FP32 [n_experts]; k experts per token.  At K_in in {1024, 2048,
  * 4096}, hidden in {1024, 2048}, n_experts <= 256, k <= 6 the whole layer is ONE kernel launch (router inside),
  * otherwise a router kernel is launched first (3 launches).  After the call the workspace holds the picks: int32 ids
- * at byte offset k * hidden * 8, FP32 weights 32 bytes further.  Return codes as mxfp4_grouped_gemv_topk_ids. */
+ * at byte offset k * hidden * 8, FP32 weights 32 bytes further.  `out` may be pinned host memory mapped on the device:
+ * the kernel's stores are then the device-to-host transfer.  Return codes as mxfp4_grouped_gemv_topk_ids. */
 int mxfp4_moe_decode_layer(const uint16_t* x, const uint8_t* bank_W1_packed, const uint8_t* bank_W3_packed,
                            const uint8_t* bank_W2_packed, const uint8_t* bank_W1_scale, const uint8_t* bank_W3_scale,
                            const uint8_t* bank_W2_scale, const float* logits, int n_experts, int score_func, float eps,
