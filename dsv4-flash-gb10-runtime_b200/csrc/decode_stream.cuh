@@ -253,6 +253,11 @@ __global__ void __launch_bounds__(kStreamThreads, 1) moe_decode_stream_kernel(co
     // stacked weights do not depend on the previous kernel in the stream: request them before waiting for it
     if (!service) prologue_claim();
     if (!use_table && !service) prologue();
+    // The logits may still be written by the previous kernel of the stream, so they are read after the wait; asking
+    // the L2 for their lines now is harmless either way (a later write lands in the same L2) and takes the miss
+    // out of the start when they are not (one 128-byte line per routing warp).
+    if (routed && warp < 8 && lane == 0 && warp * 32 < rt.n_experts)
+        asm volatile("prefetch.global.L2 [%0];" ::"l"(rt.logits + warp * 32));
     pdl_wait();
     if (warp == NW + NSV - 1 && lane == 0) s_want = ld_relaxed_gpu(sync_epoch) + 1u;
     // Router, spread over the CTA (the weight stream cannot start before the picks are known, so this is the
