@@ -161,16 +161,25 @@ def run_reference(args, rank: int):
     if frac <= 1.0 / 64 and t_probe / 64 > budget:                  # still too long at the smallest row slice:
         n_e = max(1, min(TOP_K, int(TOP_K * budget / (t_probe / 64))))   # sample fewer of the six experts too
         ids, w = ids[:n_e], w[:n_e]
-    for _ in range(args.warmup):
-        cpu_layer_sample(oracle, bank, x, ids, w, frac)
+    # every step routes like the GPU arm: softmax over 256 logits ~N(0,1), top-6 renormalised (the reference's
+    # _route); the six picks are mapped onto the six experts this arm keeps in host memory (the 3.4 GB bank of the
+    # GPU arm is not built on the host), so the bytes and the arithmetic of a step are those of the GPU arm's
+    logits = torch.randn(max(1, args.steps + args.warmup), N_EXPERTS, generator=g).numpy()
+
+    def step(i):
+        _, weights = oracle.route_softmax(logits[i:i + 1], TOP_K)
+        return cpu_layer_sample(oracle, bank, x, ids, weights[0][:len(ids)], frac)
+
+    for i in range(args.warmup):
+        step(i)
     t0 = time.perf_counter()
     covered = 0
-    for _ in range(args.steps):
-        covered += cpu_layer_sample(oracle, bank, x, ids, w, frac)
+    for i in range(args.steps):
+        covered += step(args.warmup + i)
     dt = time.perf_counter() - t0
     value = covered / dt / 1e9
-    sample = (f"{args.steps} steps, each {frac:.4f} of the rows of {len(ids)} of the layer's 6 experts "
-              f"({covered // max(1, args.steps)} B)")
+    sample = (f"{args.steps} steps, each the router (softmax, top-6) and {frac:.4f} of the rows of {len(ids)} of the "
+              f"layer's 6 experts ({covered // max(1, args.steps)} B)")
     line = {
         "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": dt / max(1, args.steps) * 1e3, "higher_is_better": True,
