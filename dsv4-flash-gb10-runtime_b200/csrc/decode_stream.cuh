@@ -512,18 +512,23 @@ __global__ void __launch_bounds__(kStreamThreads, 1) moe_decode_stream_kernel(co
                 const uint32_t slot = ring + s * L::kSlot;
                 const uint32_t lane_w = slot + lane * 16;
                 const int ea = d >> 16;
-                if (ea != cur_ea) {                              // the scale rows of this expert (requested long ago)
-                    alive = mbar_wait_limit(bars_ascale + 8 * ea, 0, 1, spin_limit);
-                    cur_ea = ea;
-                }
                 const uint32_t lane_s = ascale + (ea & 1) * L::kAScaleBuf + (d & 0xffff) * L::kRowSA + lane;
+                // the next task is claimed and described while this slot's rows are still on their way ...
+                const bool refill = (s ? tk0 : tk1) < 0;
+                int nt = 0, nd = 0;
+                if (refill) {
+                    nt = claim();
+                    nd = nt < n_total ? describe(nt) : 0;
+                }
                 alive = mbar_wait_limit(bars + 8 * s, (parity >> s) & 1u, 1, spin_limit) && alive;
                 parity ^= 1u << s;
-                // One copy in flight per warp: the slot consumed last is requested again only now that this one has
-                // landed (the bytes in flight, and with them every memory latency of the SM, stay small).
-                if ((s ? tk0 : tk1) < 0) {
-                    const int nt = claim();
-                    const int nd = nt < n_total ? describe(nt) : 0;
+                if (ea != cur_ea) {                              // the scale rows of this expert (requested long ago)
+                    alive = mbar_wait_limit(bars_ascale + 8 * ea, 0, 1, spin_limit) && alive;
+                    cur_ea = ea;
+                }
+                // ... and requested only now that this one has landed: one copy in flight per warp (the bytes in
+                // flight, and with them every memory latency of the SM, stay small).
+                if (refill) {
                     if (nt < n_total && alive) issue(nt, nd, s ^ 1);
                     if (s) { tk0 = nt; td0 = nd; } else { tk1 = nt; td1 = nd; }
                 }
@@ -568,20 +573,22 @@ __global__ void __launch_bounds__(kStreamThreads, 1) moe_decode_stream_kernel(co
                 const uint32_t slot = ring + s * L::kSlot;
                 const uint32_t lane_w = slot + lane * 16;
                 const uint32_t lane_s = bscale + (e * kStreamCap + l0) * L::kRowSB + lane;
-                if (cur_e < 0) alive = mbar_wait_limit(bar_bscale, 0, 2, spin_limit);
+                const bool refill = (s ? tk0 : tk1) < 0;       // as above: claimed early, requested late
+                int nt = 0, nd = 0;
+                if (refill) {
+                    nt = claim();
+                    nd = nt < n_total ? describe(nt) : 0;
+                }
+                alive = mbar_wait_limit(bars + 8 * s, (parity >> s) & 1u, 2, spin_limit) && alive;
+                parity ^= 1u << s;
+                if (cur_e < 0) alive = mbar_wait_limit(bar_bscale, 0, 2, spin_limit) && alive;
                 if (e != cur_e) {
                     alive = mbar_wait_limit(bars_mid + 8 * e, 0, 3, spin_limit) && !failed && alive;
                     lane_blocks_from_smem<L::kBplB>(mvec + (size_t)e * HT, lane, m2);
                     cur_scale = mid_scale[e];
                     cur_e = e;
                 }
-                alive = mbar_wait_limit(bars + 8 * s, (parity >> s) & 1u, 2, spin_limit) && alive;
-                parity ^= 1u << s;
-                // One copy in flight per warp: the slot consumed last is requested again only now that this one has
-                // landed (the bytes in flight, and with them every memory latency of the SM, stay small).
-                if ((s ? tk0 : tk1) < 0) {
-                    const int nt = claim();
-                    const int nd = nt < n_total ? describe(nt) : 0;
+                if (refill) {
                     if (nt < n_total && alive) issue(nt, nd, s ^ 1);
                     if (s) { tk0 = nt; td0 = nd; } else { tk1 = nt; td1 = nd; }
                 }
