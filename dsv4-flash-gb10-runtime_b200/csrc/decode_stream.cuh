@@ -550,7 +550,7 @@ __global__ void __launch_bounds__(kStreamThreads, 1) moe_decode_stream_kernel(co
                 if (lane == 0 && alive) {
                     const float g = v[0] * xs;
                     const uint32_t q = (uint32_t)(ea * HT + hb + (d & 0xffff));
-                    const float mid = (g / (1.0f + __expf(-g))) * up;
+                    const float mid = swiglu_f32(g, up);
                     // value and tag in one 8-byte store: a reader sees both or neither
                     st_relaxed_gpu_u64(a.mid8 + q, ((unsigned long long)stream_tag(want, q) << 32) | __float_as_uint(mid));
                     rows_done = atomicAdd(&done_a[ea], 1) + 1;   // progress: what the service warps time their copies by

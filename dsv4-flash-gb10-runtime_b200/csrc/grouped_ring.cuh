@@ -256,7 +256,7 @@ __global__ void __launch_bounds__(kRingGateWarps * 32, 1) gate_up_ring_kernel(co
                 const float up = __shfl_sync(kFullMask, v[0], 16) * xs;
                 if (lane == 0 && alive) {
                     const float g = v[0] * xs;
-                    a.mid[q0 + i * NW] = (g / (1.0f + __expf(-g))) * up;
+                    a.mid[q0 + i * NW] = swiglu_f32(g, up);
                 }
                 __syncwarp();                                        // every lane has read the slot
                 if (i + S < n_i && alive) issue(q0 + (i + S) * NW, s);

@@ -161,7 +161,7 @@ __global__ void __launch_bounds__(kGateThreads, 1) grouped_gate_up_kernel(const 
         v[1] = row_dot_refill<BPL>(u, x, cur.w3, cur.s3, more, ok);
         multi_reduce<2>(v, lane);                                // lane 0: gate sum, lane 16: up sum
         const float up = __shfl_sync(kFullMask, v[0], 16);
-        if (lane == 0) a.mid[q] = (v[0] / (1.0f + __expf(-v[0]))) * up;
+        if (lane == 0) a.mid[q] = swiglu_f32(v[0], up);
     }
 }
 
