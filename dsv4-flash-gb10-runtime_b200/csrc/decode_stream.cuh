@@ -426,7 +426,7 @@ __global__ void __launch_bounds__(kStreamThreads, 1) moe_decode_stream_kernel(co
             if (issued == finished) {
                 // nothing in flight: wait for this CTA to be far enough to expect expert `issued` complete everywhere
                 // (a timed sleep: a service warp that polls in a loop takes issue slots from its scheduler's streaming warps)
-                while (!gate_open(issued) && budget > 0) { --budget; __nanosleep(issued + 1 == a.E ? 100 : 400); }
+                while (!gate_open(issued) && budget > 0) { --budget; __nanosleep(100); }
                 gave_up = budget == 0;
                 request(issued++);
             }
