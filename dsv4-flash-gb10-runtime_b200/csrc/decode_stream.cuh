@@ -246,7 +246,6 @@ __global__ void __launch_bounds__(kStreamThreads, 1) moe_decode_stream_kernel(co
             issue_ascale(0);
             if (a.E > 1) issue_ascale(1);
         }
-        if (warp == 1 || NW == 1) issue_bscale();
     };
 
     __syncthreads();                                           // barriers and the queue are initialised
@@ -413,6 +412,14 @@ __global__ void __launch_bounds__(kStreamThreads, 1) moe_decode_stream_kernel(co
             }
             return all;
         };
+        // The down scales of all experts are not needed before the down rows.  At the start every copy queues behind
+        // the others in the SM's copy engine (about 25 ns each) and these would delay the first weight rows, so a
+        // service warp, idle until the first expert's rows are done, requests them a microsecond or two later.
+        if (sw == 0) {
+            const long long t0 = clock64();
+            while (clock64() - t0 < 4000) { }
+            issue_bscale();
+        }
         int issued = 0, finished = 0;                          // experts requested / converted
         uint32_t stage_parity = 0, attempt = 0;
         bool ok = true;
