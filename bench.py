@@ -31,7 +31,7 @@ BYTES_PER_EXPERT = 2 * (EXPERT_FF * HIDDEN // 2 + EXPERT_FF * HIDDEN // 32) + (H
 LAYER_BYTES = TOP_K * BYTES_PER_EXPERT + 2 * HIDDEN * 2                 # weights + x + out = 80 232 448
 # dram__bytes_read.sum + dram__bytes_write.sum of one moe_decode_stream_kernel<4096, 2048> launch at this shape,
 # from an ncu capture of that launch on a 64-expert bank (the traffic of a launch does not depend on the bank size)
-FUSED_DRAM_TRAFFIC = 81_940_000
+FUSED_DRAM_TRAFFIC = 82_480_000
 METRIC = "mxfp4_routed_moe_decode_hbm_throughput"
 UNIT = "GB/s"
 SEED = 1236                                                             # 1234 + index of the configuration
