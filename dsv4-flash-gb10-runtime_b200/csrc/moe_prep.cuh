@@ -275,44 +275,9 @@ __global__ void moe_ep_sum_kernel(const __nv_bfloat16* __restrict__ recv, const 
 // (K must be a multiple of 256): 16- or 32-byte loads, one 4-byte store per lane and term.
 // With PEER the rows are not in `src` but in the per-rank buffers of `in` (row t = row t % tokens_per_rank of rank
 // t / tokens_per_rank).
-
-// Three terms of the eight values a lane holds (four lanes = one 32-element block), written at element e0.
-__device__ __forceinline__ void mx3_quantize_lane8(float (&v)[8], long long e0, int lane, long long term_q, long long term_s,
-                                                   uint8_t* __restrict__ q, uint8_t* __restrict__ s) {
-#pragma unroll
-    for (int t = 0; t < 3; ++t) {
-        uint32_t m = 0;
-#pragma unroll
-        for (int i = 0; i < 8; ++i) m = max(m, __float_as_uint(v[i]) & 0x7fffffffu);
-        m = max(m, __shfl_xor_sync(kFullMask, m, 1));
-        m = max(m, __shfl_xor_sync(kFullMask, m, 2));            // 4-lane block
-        int e = (int)(m >> 23) - 127 - 2;                       // amax / 2^e in [4, 8)
-        if ((m & 0x007fffffu) > 0x00400000u) e += 1;             // above 6 * 2^e the E2M1 grid would saturate
-        e = min(max(e, -127), 127);
-        if (m == 0) e = -127;
-        const float inv = __uint_as_float((uint32_t)min(max(127 - e, 1), 254) << 23);
-        const float sc = __uint_as_float((uint32_t)max(e + 127, 1) << 23);                     // 2^e (>= 2^-126)
-        uint32_t word = 0;
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-            uint16_t packed;
-            asm("{\n .reg .b8 b;\n cvt.rn.satfinite.e2m1x2.f32 b, %2, %1;\n mov.b16 %0, {b, 0};\n}"
-                : "=h"(packed) : "f"(v[2 * i] * inv), "f"(v[2 * i + 1] * inv));
-            const float2 back = e2m1x2_to_float2(packed);
-            v[2 * i] -= back.x * sc;
-            v[2 * i + 1] -= back.y * sc;
-            word |= (uint32_t)(packed & 0xff) << (8 * i);
-        }
-        *reinterpret_cast<uint32_t*>(q + t * term_q + (e0 >> 1)) = word;
-        if ((lane & 3) == 0) s[t * term_s + (e0 >> 5)] = (uint8_t)(e + 127);
-    }
-}
-
 // rows_used (device, may be null): only rows [0, *rows_used) are converted (the intermediate of an expert-parallel
 // rank holds rows for its own pairs only).  row_ids / k (may be null): row t is converted only if one of
 // row_ids[t * k .. t * k + k) is >= 0 (a token none of whose experts lives on this rank is never read).
-// bf16 rows: a warp has the loads of four chunks in flight before it converts the first (rows read from another
-// rank cross NVLink, and one dependent load per warp at a time left the links idle).
 template <class Elem, bool PEER = false>
 __global__ void moe_quantize_mxfp4x3_kernel(const Elem* __restrict__ src, long long rows, int K,
                                             uint8_t* __restrict__ q, uint8_t* __restrict__ s, const MoePeerIn in = {},
@@ -324,61 +289,62 @@ __global__ void moe_quantize_mxfp4x3_kernel(const Elem* __restrict__ src, long l
     const long long live_rows = rows_used ? min(rows, (long long)__ldg(rows_used)) : rows;
     const long long n_chunks = live_rows * (K / 256);
     const long long term_q = rows * (K / 2), term_s = rows * (K / 32);
-    const long long first = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
-    const long long stride = (long long)gridDim.x * (blockDim.x >> 5);
-    if constexpr (sizeof(Elem) == 2) {
-        constexpr int U = 4;
-        for (long long w0 = first; w0 < n_chunks; w0 += stride * U) {
-            uint4 raw[U];
-            bool ok[U];
-#pragma unroll
-            for (int u = 0; u < U; ++u) {
-                const long long w = w0 + u * stride;
-                const long long e0 = w * 256 + 8 * lane;             // first of this lane's eight elements (row-major)
-                ok[u] = w < n_chunks;
-                if (ok[u] && row_ids) {
-                    const long long row = e0 / K;
-                    bool wanted = false;
-                    for (int j = 0; j < k; ++j) wanted |= __ldg(row_ids + row * k + j) >= 0;
-                    ok[u] = wanted;                                  // warp-uniform: a warp works on one row
-                }
-                if (ok[u]) {
-                    const Elem* from = src + e0;
-                    if constexpr (PEER) {
-                        const long long row = e0 / K;
-                        const int r = (int)(row / in.tokens_per_rank);
-                        from = reinterpret_cast<const Elem*>(in.x[r]) + (row - (long long)r * in.tokens_per_rank) * K + (e0 - row * K);
-                    }
-                    raw[u] = __ldcs(reinterpret_cast<const uint4*>(from));
-                }
-            }
-#pragma unroll
-            for (int u = 0; u < U; ++u) {
-                if (!ok[u]) continue;
-                const long long e0 = (w0 + u * stride) * 256 + 8 * lane;
-                const uint32_t uu[4] = {raw[u].x, raw[u].y, raw[u].z, raw[u].w};
-                float v[8];
-#pragma unroll
-                for (int i = 0; i < 4; ++i) {
-                    v[2 * i] = __uint_as_float(uu[i] << 16);
-                    v[2 * i + 1] = __uint_as_float(uu[i] & 0xffff0000u);
-                }
-                mx3_quantize_lane8(v, e0, lane, term_q, term_s, q, s);
-            }
+    for (long long w = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); w < n_chunks;
+         w += (long long)gridDim.x * (blockDim.x >> 5)) {
+        const long long e0 = w * 256 + 8 * lane;                    // first of this lane's eight elements (row-major)
+        if (row_ids) {
+            const long long row = e0 / K;
+            bool wanted = false;
+            for (int j = 0; j < k; ++j) wanted |= __ldg(row_ids + row * k + j) >= 0;
+            if (!wanted) continue;                                   // warp-uniform: a warp works on one row
         }
-    } else {
-        for (long long w = first; w < n_chunks; w += stride) {
-            const long long e0 = w * 256 + 8 * lane;
-            if (row_ids) {
+        float v[8];
+        if constexpr (sizeof(Elem) == 2) {
+            const Elem* from = src + e0;
+            if constexpr (PEER) {
                 const long long row = e0 / K;
-                bool wanted = false;
-                for (int j = 0; j < k; ++j) wanted |= __ldg(row_ids + row * k + j) >= 0;
-                if (!wanted) continue;
+                const int r = (int)(row / in.tokens_per_rank);
+                from = reinterpret_cast<const Elem*>(in.x[r]) + (row - (long long)r * in.tokens_per_rank) * K + (e0 - row * K);
             }
+            const uint4 u = __ldcs(reinterpret_cast<const uint4*>(from));
+            const uint32_t uu[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                v[2 * i] = __uint_as_float(uu[i] << 16);
+                v[2 * i + 1] = __uint_as_float(uu[i] & 0xffff0000u);
+            }
+        } else {
             const float4 f0 = __ldcs(reinterpret_cast<const float4*>(src + e0));
             const float4 f1 = __ldcs(reinterpret_cast<const float4*>(src + e0) + 1);
-            float v[8] = {f0.x, f0.y, f0.z, f0.w, f1.x, f1.y, f1.z, f1.w};
-            mx3_quantize_lane8(v, e0, lane, term_q, term_s, q, s);
+            v[0] = f0.x; v[1] = f0.y; v[2] = f0.z; v[3] = f0.w;
+            v[4] = f1.x; v[5] = f1.y; v[6] = f1.z; v[7] = f1.w;
+        }
+#pragma unroll
+        for (int t = 0; t < 3; ++t) {
+            uint32_t m = 0;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) m = max(m, __float_as_uint(v[i]) & 0x7fffffffu);
+            m = max(m, __shfl_xor_sync(kFullMask, m, 1));
+            m = max(m, __shfl_xor_sync(kFullMask, m, 2));            // 4-lane block
+            int e = (int)(m >> 23) - 127 - 2;                       // amax / 2^e in [4, 8)
+            if ((m & 0x007fffffu) > 0x00400000u) e += 1;             // above 6 * 2^e the E2M1 grid would saturate
+            e = min(max(e, -127), 127);
+            if (m == 0) e = -127;
+            const float inv = __uint_as_float((uint32_t)min(max(127 - e, 1), 254) << 23);
+            const float sc = __uint_as_float((uint32_t)max(e + 127, 1) << 23);                     // 2^e (>= 2^-126)
+            uint32_t word = 0;
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                uint16_t packed;
+                asm("{\n .reg .b8 b;\n cvt.rn.satfinite.e2m1x2.f32 b, %2, %1;\n mov.b16 %0, {b, 0};\n}"
+                    : "=h"(packed) : "f"(v[2 * i] * inv), "f"(v[2 * i + 1] * inv));
+                const float2 back = e2m1x2_to_float2(packed);
+                v[2 * i] -= back.x * sc;
+                v[2 * i + 1] -= back.y * sc;
+                word |= (uint32_t)(packed & 0xff) << (8 * i);
+            }
+            *reinterpret_cast<uint32_t*>(q + t * term_q + (e0 >> 1)) = word;
+            if ((lane & 3) == 0) s[t * term_s + (e0 >> 5)] = (uint8_t)(e + 127);
         }
     }
 }
