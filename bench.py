@@ -291,16 +291,20 @@ def batched_configs(rt, qz, torch, dist, bank, dev, rank, world):
 
         y = step()
         torch.cuda.synchronize()
-        parity = None
+        parity, parity_by = None, None
         if world > 1:
             ref = rt.moe_forward(bank, x_l, ids_l, w_l).float()
-            parity = float((y.float() - ref).abs().max() / ref.abs().max())
-            for other in ([step_a2a, step_gathered, step_peer_combine] if equal else []):
+            per = [float((y.float() - ref).abs().max() / ref.abs().max())]
+            names = ["primary"]
+            for label, other in ([("all_to_all", step_a2a), ("gather_reduce_scatter", step_gathered),
+                                  ("all_gather_then_peer_combine", step_peer_combine)] if equal else []):
                 y2 = other()
-                parity = max(parity, float((y2.float() - ref).abs().max() / ref.abs().max()))
-            t = torch.tensor([parity], device=dev, dtype=torch.float64)
-            dist.all_reduce(t, op=dist.ReduceOp.MAX)
-            parity = float(t.item())
+                per.append(float((y2.float() - ref).abs().max() / ref.abs().max()))
+                names.append(label)
+            t = torch.tensor(per, device=dev, dtype=torch.float64)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)             # every formulation: the worst rank
+            parity_by = dict(zip(names, (float(v) for v in t.tolist())))
+            parity = max(parity_by.values())
         ms = timed_ms(step)
         ms_a2a = timed_ms(step_a2a) if world > 1 and equal else None
         ms_gathered = timed_ms(step_gathered) if world > 1 and equal else None
@@ -340,6 +344,7 @@ def batched_configs(rt, qz, torch, dist, bank, dev, rank, world):
                      "frac_of_measured_hbm_peak": min_bytes / ms / 1e6 / world / measured_hbm_peak()[0],
                      "gbs_min_bytes": min_bytes / ms / 1e6, "distinct_experts": distinct,
                      "max_abs_vs_1gpu_over_inf_norm": parity,
+                     "max_abs_vs_1gpu_over_inf_norm_by_formulation": parity_by,
                      "stage_us_one_timed_call_max_over_ranks": stage_us,
                      "exchange": "none" if world == 1 else
                      ("peer memory over NVLink on both sides (symmetric memory, no collective library): tokens read by the "
@@ -886,6 +891,7 @@ def run_gpu(args, rank: int, world: int, local_rank: int):
         if world > 1:      # the expert-parallel results of configurations 3 and 4 at this N, with their parity
             line["ep"] = {name: {"n_gpus": world, "ms": b["ms"], "tflops": b["tflops"], "gbs_min_bytes": b["gbs_min_bytes"],
                                  "max_abs_vs_1gpu_over_inf_norm": b["max_abs_vs_1gpu_over_inf_norm"],
+                                 "max_abs_vs_1gpu_over_inf_norm_by_formulation": b["max_abs_vs_1gpu_over_inf_norm_by_formulation"],
                                  "ms_all_to_all_variant": b["ms_all_to_all_variant"],
                                  "ms_gather_reduce_scatter_variant": b["ms_gather_reduce_scatter_variant"],
                                  "ms_all_gather_then_peer_combine_variant": b["ms_all_gather_then_peer_combine_variant"],
